@@ -1,0 +1,139 @@
+/* mk_kv.h -- C ABI of the B200 KV-cache hot path (libmk_kv.so).
+ *
+ * Drop-in boundary for the KV path of the reference engine. The reference's own exported API (capi.cpp:261-802) is
+ * token-level; its KV path is reached through the engine object. This header keeps the reference's names, return codes,
+ * ownership and threading rules for every KV-relevant call it exports, and adds the tensor-level calls (mk_kv_*) that
+ * the reference performs inside its decode cycle. Each declaration cites what it replaces (paths relative to the
+ * reference project root).
+ *
+ * Conventions (capi.cpp:201-263):
+ *   - every call catches all C++ exceptions: it returns -1 (or NULL) and the message is read with mk_last_error(), which is
+ *     thread-local;
+ *   - a failed CUDA call resets the engine before -1 is returned; a sticky CUDA error ends the process with exit code 4;
+ *   - the caller owns every out-buffer and passes its capacity; out = NULL, cap = 0 returns the needed count;
+ *   - one engine thread per handle; a handle binds to the CUDA device current at mk_kv_new;
+ *   - K, V, Q, O are DEVICE pointers unless a parameter says "host"; no call allocates on behalf of the caller.
+ *
+ * Sequences: seq = MK_SEQ_MAIN (-1) is the engine's own sequence; 0 .. n-1 are the parallel slots opened by mk_slots_open.
+ * Shapes: 24 query heads, 4 kv heads, head dimension 256 (mk_shared.cuh:215); at most 8 query tokens per call.
+ */
+#ifndef MK_KV_H
+#define MK_KV_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MK_SEQ_MAIN (-1)
+/* mk_kv_new flags */
+#define MK_KV_SPILL 1   /* main-format rows are written when a position leaves the q8_0 window (fp16 shadow of the ring), not at append */
+#define MK_KV_WIN_ALL 2 /* rings for the 8-bit sides too: MK_KV_WIN_ALL test knob, loader.cu:1487-1490 */
+#define MK_KV_EXACT 4   /* checkpoints keep a copy of the window rings: MK_EXACT, ck_pool.cu:135-158 */
+
+/* capi.cpp:263 */
+const char * mk_last_error(void);
+/* ABI check for bindings: a hash of the shapes and struct sizes this build uses (mk_shared.cuh:582-593 mk_abi_sig) */
+unsigned long long mk_kv_abi_sig(void);
+/* capi.cpp:787-800 */
+const char * mk_build_info(void);
+
+/* Replaces mk_new / mk_new2 (capi.cpp:266-312) for the KV path: instead of a model file, the shapes and the reference's
+ * MK_KV / MK_KV_WIN settings (loader.cu:1329-1366, 1478-1503). layers: attention layers (1 .. 17); ctx: positions per
+ * sequence; kv_spec: e.g. "K*=5r,V*=6" (NULL / "": q8_0); kv_win: e.g. 2048 (0: no window). NULL on error. */
+void * mk_kv_new(int layers, int ctx, const char * kv_spec, int kv_win, int flags);
+/* capi.cpp:418-424 */
+void mk_free(void * h);
+/* capi.cpp:564-569: clears every sequence (an error is only visible through mk_last_error) */
+void mk_reset(void * h);
+/* All later launches go to this cudaStream_t (default: the legacy default stream, as the reference: engine_impl.h:327) */
+int mk_kv_set_stream(void * h, void * cuda_stream);
+/* Waits for the engine's streams; -1 if a kernel reported a wait that ran out (the engine is reset) */
+int mk_kv_sync(void * h);
+
+/* ---- the hot path ---- */
+/* The reference's K / V row jobs (qwen38_mk.cu:2892-2926) and pk_attn_prep's store part (prefill.cuh:984-1023):
+ * rows pos0 .. pos0 + n - 1 of one layer from fp16 K, V [n][4][256] (post-norm, post-RoPE). Rows at or past the committed
+ * length may be rewritten. 0 / -1 */
+int mk_kv_append(void * h, int seq, int layer, int pos0, int n, const void * K, const void * V);
+/* attn_core + attn_combine (qwen38_mk.cu:4555-4690) without the model's gate: T query tokens at positions n .. n + T - 1
+ * (their rows already appended), causal among the T. Q fp16 [T][24][256] (post-norm, post-RoPE, unscaled), O fp32
+ * [T][24][256]. 0 / -1 */
+int mk_kv_attend(void * h, int seq, int layer, int n, int T, const void * Q, void * O);
+/* append + attend of one decode step's layer, as the reference's attention phase does in one pass */
+int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O);
+/* lanes_step (lanes.cu:452-560): one pass over several sequences; job j runs T[j] tokens at n[j] of sequence seqs[j].
+ * K, V [sum T][4][256], Q [sum T][24][256], O [sum T][24][256] packed in job order. seqs, n, T are host arrays.
+ * mk_kv_reserve_batch(njobs) must have been called once with at least this many jobs. */
+int mk_kv_reserve_batch(void * h, int njobs);
+int mk_kv_step_batch(void * h, int njobs, const int * seqs, int layer, const int * n, const int * T, const void * K, const void * V,
+                     const void * Q, void * O);
+int mk_kv_attend_batch(void * h, int njobs, const int * seqs, int layer, const int * n, const int * T, const void * Q, void * O);
+/* The step's accepted count (engine.cu:1353-1413): the sequence is positions 0 .. len - 1 from now on */
+int mk_kv_commit(void * h, int seq, int len);
+int mk_kv_position(void * h, int seq);
+/* att_cap_T (mk_shared.cuh:288-291): the most tokens a call at position n may carry so its rows share one partition */
+int mk_kv_cap_T(int n, int T_req);
+
+/* ---- rewind (main sequence: the reference's names; any sequence: the mk_kv_ forms) ---- */
+/* capi.cpp:571-576 */
+int mk_truncate(void * h, int len);
+int mk_kv_truncate(void * h, int seq, int len);
+/* Saves a checkpoint at the committed position (the reference saves them during a prefill: qwen38_mk.h:57-64); returns the position */
+int mk_kv_checkpoint(void * h, int seq);
+/* capi.cpp:593-599 */
+int mk_checkpoints(void * h, int * out, int cap);
+int mk_kv_checkpoints(void * h, int seq, int * out, int cap);
+/* capi.cpp:600-603: 0, or -1 (no checkpoint there) */
+int mk_rewind_to(void * h, int pos);
+int mk_kv_rewind_to(void * h, int seq, int pos);
+
+/* ---- conversation state in pinned host memory (capi.cpp:644-741) ---- */
+int mk_store_budget(void * h, long long bytes);
+int mk_store_reserve(void * h, long long bytes);
+/* out[0..9]: budget, allocated, used bytes, parked entries, last copy's bytes and microseconds, side request's copy-out
+ * microseconds, bytes per KV token, 0, 0 */
+int mk_store_info(void * h, long long * out, int cap);
+void mk_kv_sizes(void * h, long long * per_token, long long * rings, long long * state, long long * checkpoint);
+/* id > 0, 0 (empty sequence), -3 (no room in the store), -1 error */
+int mk_park(void * h, int max_checkpoints);
+int mk_kv_park(void * h, int seq, int max_checkpoints);
+/* 0, or -1 (no such entry / error) */
+int mk_unpark(void * h, int id);
+int mk_kv_unpark(void * h, int seq, int id);
+int mk_park_drop(void * h, int id);
+long long mk_park_need(void * h, int max_checkpoints);
+long long mk_park_bytes(void * h, int id);
+/* Rows [0, pos) of parked entry id become the sequence (the entry stays parked); the window rings of those positions are
+ * rebuilt from the main rows exactly as mk_unpark followed by mk_rewind_to(pos) without a ring snapshot leaves them
+ * (host_store.cu:457-483, ck_pool.cu:285-296). wait = 0 returns once the copies are enqueued on the side stream; later
+ * launches on the sequence wait for them on the GPU, mk_kv_store_wait waits on the host. 0 / -1 */
+int mk_kv_restore_prefix(void * h, int seq, int id, int pos, int wait);
+int mk_kv_store_wait(void * h);
+/* capi.cpp:683-711 */
+int mk_side_begin(void * h);
+int mk_side_end(void * h);
+int mk_side_drop(void * h);
+int mk_side_active(void * h);
+
+/* ---- parallel slots (capi.cpp mk_slots_open; lanes.cu:291-326): n sequences of ctx positions each; returns ctx ---- */
+int mk_slots_open(void * h, int n, int ctx);
+int mk_slots_count(void * h);
+
+/* ---- test helpers ---- */
+/* capi.cpp:635-642 (state_digest, engine.cu:1438-1500: KV words) */
+int mk_state_digest(void * h, unsigned long long * out, int cap);
+long long mk_kv_state_digest(void * h, int seq, unsigned long long * out, long long cap);
+/* One row's bytes to HOST buffers: ring = 0 the main row of position pos (32 * bits value bytes), ring = 1 ring row pos
+ * (256 bytes); sc receives the 8 fp16 scales. Returns the value bytes, -1 on error */
+int mk_kv_read_row(void * h, int seq, int layer, int side, int kv_head, int pos, int ring, void * val, void * sc);
+int mk_kv_write_row(void * h, int seq, int layer, int side, int kv_head, int pos, int ring, const void * val, const void * sc);
+/* format facts: bits of a side (0 K, 1 V) of a layer, 1 if it has a ring, ring rows per kv head, device bytes held */
+int mk_kv_bits(void * h, int side, int layer);
+int mk_kv_has_ring(void * h, int side, int layer);
+int mk_kv_ring_rows(void * h);
+long long mk_kv_device_bytes(void * h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,1034 @@
+// KvEngine implementation: see kv_engine.h. Host logic only; every device operation is a launcher from kv_kernels.h or a
+// CUDA runtime copy. Compute runs on the engine's stream; snapshot / restore copies run on a side stream and are tied to
+// the compute stream by events.
+#include "kv_engine.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+namespace mkkv {
+
+// A sticky error means the context is lost: nothing can be reset, the process ends with code 4 as the reference does
+// (mk_shared.cuh:170-198). Everything else becomes MKCudaError and the C API resets the engine.
+static bool context_lost(cudaError_t e) {
+    switch (e) {
+    case cudaErrorIllegalAddress:
+    case cudaErrorLaunchFailure:
+    case cudaErrorIllegalInstruction:
+    case cudaErrorMisalignedAddress:
+    case cudaErrorInvalidAddressSpace:
+    case cudaErrorInvalidPc:
+    case cudaErrorHardwareStackError:
+    case cudaErrorLaunchTimeout:
+    case cudaErrorECCUncorrectable:
+    case cudaErrorAssert:
+    case cudaErrorDevicesUnavailable:
+        return true;
+    default:
+        return false;
+    }
+}
+void cuda_fail(cudaError_t e, const char * what, const char * file, int line) {
+    char msg[512];
+    snprintf(msg, sizeof msg, "CUDA error %s (%s) at %s:%d", cudaGetErrorString(e), what, file, line);
+    cudaGetLastError();
+    // sticky = the context is lost: the error repeats after it was cleared (the reference's test, mk_shared.cuh:170-198)
+    if (context_lost(e) || context_lost(cudaDeviceSynchronize())) {
+        fprintf(stderr, "[mk] sticky %s: exiting with code 4\n", msg);
+        fflush(stderr);
+        std::_Exit(4);
+    }
+    cudaGetLastError();
+    throw MKCudaError(msg);
+}
+
+namespace {
+bool parse_spec(const std::string & str, int layers, int (*kvb)[MAX_LAYERS], int (*rot)[MAX_LAYERS]) {
+    // MK_KV grammar: comma-separated <K|V|*><layer|*|empty>=<4..8>[r] (loader.cu:1329-1366)
+    size_t i = 0;
+    while (i < str.size()) {
+        size_t j = str.find(',', i);
+        if (j == std::string::npos) j = str.size();
+        const std::string tok = str.substr(i, j - i);
+        i = j + 1;
+        if (tok.empty()) continue;
+        const size_t e = tok.find('=');
+        if (e == std::string::npos || e == 0 || !strchr("KV*", tok[0])) throw std::runtime_error("MK_KV: bad item " + tok);
+        const std::string sl = tok.substr(1, e - 1), md = tok.substr(e + 1);
+        if (md.empty() || md.size() > 2 || md[0] < '4' || md[0] > '8' || (md.size() == 2 && md[1] != 'r'))
+            throw std::runtime_error("MK_KV: expected 4..8 or 4r..8r in " + tok);
+        const bool r = md.size() == 2, all = sl.empty() || sl == "*";
+        char * end = nullptr;
+        const long slot = all ? -1 : strtol(sl.c_str(), &end, 10);
+        if (!all && (*end || slot < 0 || slot >= layers))
+            throw std::runtime_error("MK_KV: bad slot in " + tok + " (0.." + std::to_string(layers - 1) + " or *)");
+        for (int w = 0; w < 2; w++)
+            if (tok[0] == '*' || tok[0] == "KV"[w])
+                for (int s = 0; s < layers; s++)
+                    if (all || s == slot) {
+                        kvb[w][s] = md[0] - '0';
+                        rot[w][s] = r;
+                    }
+    }
+    return true;
+}
+double ms_since(std::chrono::steady_clock::time_point t0) {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+}
+} // namespace
+
+KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
+    if (cfg.layers < 1 || cfg.layers > MAX_LAYERS) throw std::runtime_error("layers must be 1.." + std::to_string(MAX_LAYERS));
+    if (cfg.ctx < 1) throw std::runtime_error("ctx must be positive");
+    for (int w = 0; w < 2; w++)
+        for (int s = 0; s < MAX_LAYERS; s++) {
+            kvb_[w][s] = 8;
+            rot_[w][s] = 0;
+            ring_[w][s] = false;
+        }
+    parse_spec(cfg.kv_spec, cfg.layers, kvb_, rot_);
+    // the window needs a format spec, as in the reference (loader.cu:1478)
+    if (cfg.kv_spec.empty() || cfg.win <= 0) cfg_.win = 0;
+    rc_ = kv_ring_rows(cfg_.win);
+    for (int w = 0; w < 2; w++)
+        for (int s = 0; s < cfg.layers; s++) ring_[w][s] = cfg_.win > 0 && (kvb_[w][s] != 8 || cfg.win_all);
+    if (cfg_.win <= 0) cfg_.spill = false;
+    MKKV_CK(cudaGetDevice(&dev_));
+    MKKV_CK(cudaStreamCreateWithFlags(&st_copy_, cudaStreamNonBlocking));
+    MKKV_CK(cudaEventCreateWithFlags(&ev_compute_, cudaEventDisableTiming));
+    MKKV_CK(cudaEventCreateWithFlags(&ev_copy_, cudaEventDisableTiming));
+    MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&h_status_), sizeof(int), cudaHostAllocMapped));
+    *h_status_ = 0;
+    MKKV_CK(cudaHostGetDevicePointer(reinterpret_cast<void **>(&d_status_), h_status_, 0));
+    if (const char * c = getenv("MK_STORE_CHUNK_MIB")) {
+        const long v = atol(c);
+        if (v >= 1 && v <= 1024) hs_chunk_ = (size_t) v << 20;
+    }
+    alloc_seq(main_, cfg.ctx);
+    ensure_work(NKV * ATT_NCH, 1);
+}
+
+KvEngine::~KvEngine() {
+    cudaSetDevice(dev_);
+    cudaDeviceSynchronize();
+    free_seq(main_);
+    for (auto & s : slots_) free_seq(s);
+    for (auto & p : parked_)
+        for (char * c : p.second.blob.chunks) cudaFreeHost(c);
+    for (char * c : sw_blob_.chunks) cudaFreeHost(c);
+    for (char * c : hs_free_) cudaFreeHost(c);
+    for (auto & k : sw_cks_)
+        if (k.ring) cudaFreeHost(k.ring);
+    cudaFree(part_);
+    cudaFree(ml_);
+    cudaFree(d_jobs_);
+    cudaFreeHost(h_jobs_);
+    cudaFree(d_ajobs_);
+    cudaFreeHost(h_ajobs_);
+    cudaFree(staging_);
+    cudaFreeHost(h_status_);
+    cudaEventDestroy(ev_compute_);
+    cudaEventDestroy(ev_copy_);
+    cudaStreamDestroy(st_copy_);
+}
+
+void KvEngine::use_device() const { MKKV_CK(cudaSetDevice(dev_)); }
+void KvEngine::check_layer(int layer) const {
+    if (layer < 0 || layer >= cfg_.layers) throw std::runtime_error("layer " + std::to_string(layer) + " out of range");
+}
+KvEngine::Seq & KvEngine::seq_ref(int seq) {
+    if (seq == SEQ_MAIN) return main_;
+    if (seq < 0 || seq >= (int) slots_.size()) throw std::runtime_error("no sequence slot " + std::to_string(seq));
+    return slots_[seq];
+}
+const KvEngine::Seq & KvEngine::seq_ref(int seq) const { return const_cast<KvEngine *>(this)->seq_ref(seq); }
+
+void KvEngine::alloc_seq(Seq & s, int ctx) {
+    s.ctx = ctx;
+    s.ctxp = ctx + KV_PAD;
+    const size_t rows = (size_t) NKV * s.ctxp;
+    size_t vb[2] = {0, 0};
+    int nring = 0;
+    for (int w = 0; w < 2; w++)
+        for (int l = 0; l < cfg_.layers; l++) {
+            vb[w] += rows * row_bytes(kvb_[w][l]);
+            nring += ring_[w][l];
+        }
+    try {
+        for (int w = 0; w < 2; w++) {
+            MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&s.val[w]), vb[w]));
+            MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&s.sc[w]), (size_t) cfg_.layers * rows * SCALE_ROW));
+            MKKV_CK(cudaMemsetAsync(s.val[w], 0, vb[w], stream_));
+            MKKV_CK(cudaMemsetAsync(s.sc[w], 0, (size_t) cfg_.layers * rows * SCALE_ROW, stream_));
+            dev_bytes_ += vb[w] + (size_t) cfg_.layers * rows * SCALE_ROW;
+        }
+        const size_t rrows = (size_t) nring * NKV * rc_;
+        if (rrows) {
+            MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&s.ring_val), rrows * HD));
+            MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&s.ring_sc), rrows * SCALE_ROW));
+            MKKV_CK(cudaMemsetAsync(s.ring_val, 0, rrows * HD, stream_));
+            MKKV_CK(cudaMemsetAsync(s.ring_sc, 0, rrows * SCALE_ROW, stream_));
+            dev_bytes_ += rrows * (HD + SCALE_ROW);
+            if (cfg_.spill) {
+                MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&s.shadow), rrows * HD * 2));
+                MKKV_CK(cudaMemsetAsync(s.shadow, 0, rrows * HD * 2, stream_));
+                dev_bytes_ += rrows * HD * 2;
+            }
+        }
+        s.views.assign(cfg_.layers, KvView{});
+        s.regions.clear();
+        size_t off[2] = {0, 0};
+        int ri = 0;
+        std::vector<CopyRegion> ring_regions;
+        for (int l = 0; l < cfg_.layers; l++) {
+            KvView & v = s.views[l];
+            v.ctxp = s.ctxp;
+            v.rc = rc_;
+            v.win = cfg_.win;
+            v.eager = cfg_.spill ? 0 : 1;
+            for (int w = 0; w < 2; w++) { // layers packed one after another in each side's allocation (loader.cu:1457-1468)
+                KvSide & sd = v.s[w];
+                sd.bits = kvb_[w][l];
+                sd.rot = rot_[w][l];
+                sd.val = s.val[w] + off[w];
+                sd.sc = s.sc[w] + (size_t) l * rows * 8;
+                off[w] += rows * row_bytes(sd.bits);
+                sd.rval = nullptr;
+                sd.rsc = nullptr;
+                sd.shadow = nullptr;
+                if (ring_[w][l]) {
+                    sd.rval = s.ring_val + (size_t) ri * NKV * rc_ * HD;
+                    sd.rsc = s.ring_sc + (size_t) ri * NKV * rc_ * 8;
+                    if (s.shadow) sd.shadow = s.shadow + (size_t) ri * NKV * rc_ * HD;
+                    ri++;
+                }
+                for (int g = 0; g < NKV; g++) {
+                    s.regions.push_back({sd.val + (size_t) g * s.ctxp * row_bytes(sd.bits), (unsigned) row_bytes(sd.bits), 0u});
+                    s.regions.push_back({reinterpret_cast<uint8_t *>(sd.sc + (size_t) g * s.ctxp * 8), (unsigned) SCALE_ROW, 0u});
+                    if (sd.rval) {
+                        ring_regions.push_back({sd.rval + (size_t) g * rc_ * HD, (unsigned) HD, 1u});
+                        ring_regions.push_back({reinterpret_cast<uint8_t *>(sd.rsc + (size_t) g * rc_ * 8), (unsigned) SCALE_ROW, 1u});
+                    }
+                }
+            }
+        }
+        s.regions.insert(s.regions.end(), ring_regions.begin(), ring_regions.end());
+        MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&s.d_views), sizeof(KvView) * cfg_.layers));
+        MKKV_CK(cudaMemcpy(s.d_views, s.views.data(), sizeof(KvView) * cfg_.layers, cudaMemcpyHostToDevice));
+        MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&s.d_regions), sizeof(CopyRegion) * s.regions.size()));
+        MKKV_CK(cudaMemcpy(s.d_regions, s.regions.data(), sizeof(CopyRegion) * s.regions.size(), cudaMemcpyHostToDevice));
+        MKKV_CK(cudaEventCreateWithFlags(&s.copy_done, cudaEventDisableTiming));
+        MKKV_CK(cudaStreamSynchronize(stream_));
+    } catch (...) {
+        free_seq(s);
+        throw;
+    }
+    s.n = s.kv_top = 0;
+    s.spilled.assign(cfg_.layers, 0);
+    s.cks.clear();
+}
+
+void KvEngine::free_seq(Seq & s) {
+    for (int w = 0; w < 2; w++) {
+        cudaFree(s.val[w]);
+        cudaFree(s.sc[w]);
+        s.val[w] = nullptr;
+        s.sc[w] = nullptr;
+    }
+    cudaFree(s.ring_val);
+    cudaFree(s.ring_sc);
+    cudaFree(s.shadow);
+    cudaFree(s.d_views);
+    cudaFree(s.d_regions);
+    s.ring_val = nullptr;
+    s.ring_sc = nullptr;
+    s.shadow = nullptr;
+    s.d_views = nullptr;
+    s.d_regions = nullptr;
+    for (auto & k : s.cks)
+        if (k.ring) cudaFreeHost(k.ring);
+    s.cks.clear();
+    if (s.copy_done) cudaEventDestroy(s.copy_done);
+    s.copy_done = nullptr;
+}
+
+void KvEngine::sync() {
+    use_device();
+    MKKV_CK(cudaStreamSynchronize(stream_));
+    MKKV_CK(cudaStreamSynchronize(st_copy_));
+    copies_in_flight_ = false;
+    if (*h_status_ != KS_OK) {
+        const int st = *h_status_;
+        *h_status_ = KS_OK;
+        throw MKCudaError("a kernel gave up waiting for its staged tiles (status " + std::to_string(st) + ")");
+    }
+}
+
+int KvEngine::slots_open(int n, int ctx) {
+    use_device();
+    if (n < 0 || n > 1024) throw std::runtime_error("slots_open: n out of range");
+    if (ctx <= 0) ctx = cfg_.ctx;
+    sync();
+    for (auto & s : slots_) free_seq(s);
+    slots_.clear();
+    slots_.resize(n);
+    try {
+        for (auto & s : slots_) alloc_seq(s, ctx);
+    } catch (...) {
+        for (auto & s : slots_) free_seq(s);
+        slots_.clear();
+        throw;
+    }
+    return ctx;
+}
+
+void KvEngine::drop_checkpoints(Seq & s, int after) {
+    for (size_t i = 0; i < s.cks.size();)
+        if (s.cks[i].pos > after) {
+            if (s.cks[i].ring) cudaFreeHost(s.cks[i].ring);
+            s.cks.erase(s.cks.begin() + i);
+        } else i++;
+}
+
+void KvEngine::reset(int seq) {
+    Seq & s = seq_ref(seq);
+    s.n = s.kv_top = 0;
+    std::fill(s.spilled.begin(), s.spilled.end(), 0);
+    drop_checkpoints(s, -1);
+    s.failed = false;
+}
+void KvEngine::reset_all() {
+    reset(SEQ_MAIN);
+    for (int i = 0; i < (int) slots_.size(); i++) reset(i);
+    if (sw_on_) {
+        sw_on_ = false;
+        hs_release(sw_blob_);
+        for (auto & k : sw_cks_)
+            if (k.ring) cudaFreeHost(k.ring);
+        sw_cks_.clear();
+        sw_pieces_.clear();
+    }
+}
+int KvEngine::position(int seq) const { return seq_ref(seq).n; }
+int KvEngine::kv_top(int seq) const { return seq_ref(seq).kv_top; }
+void KvEngine::commit(int seq, int len) {
+    Seq & s = seq_ref(seq);
+    if (len < 0 || len > s.kv_top) throw std::runtime_error("commit: length " + std::to_string(len) + " beyond the rows written (" + std::to_string(s.kv_top) + ")");
+    s.n = len;
+}
+
+void KvEngine::wait_copies(Seq & s) {
+    if (s.copy_pending) {
+        MKKV_CK(cudaStreamWaitEvent(stream_, s.copy_done, 0));
+        s.copy_pending = false;
+    }
+}
+
+// spill mode: main-format rows of positions [spilled, upto) of one layer from the fp16 shadow
+void KvEngine::spill_to(Seq & s, int layer, int upto) {
+    if (!cfg_.spill || upto <= s.spilled[layer]) return;
+    MKKV_CK(launch_spill(s.d_views + layer, 1, s.spilled[layer], upto, stream_));
+    s.spilled[layer] = upto;
+}
+
+void KvEngine::append(int seq, int layer, int pos0, int n, const void * K, const void * V) {
+    use_device();
+    check_layer(layer);
+    Seq & s = seq_ref(seq);
+    if (n < 0 || pos0 < 0 || (long long) pos0 + n > s.ctx) throw std::runtime_error("append: rows " + std::to_string(pos0) + " + " + std::to_string(n) + " exceed the context " + std::to_string(s.ctx));
+    if (n == 0) return;
+    if (!K || !V) throw std::runtime_error("append: null K / V");
+    if (seq == SEQ_MAIN && sw_on_) sw_need(pos0 + n);
+    wait_copies(s);
+    const uint16_t * k = static_cast<const uint16_t *>(K), * v = static_cast<const uint16_t *>(V);
+    if (cfg_.spill && rc_ > 0) {
+        // a row's shadow slot is reused by the position rc later: rows about to be displaced are spilled first, and a long
+        // run is cut into pieces of at most one ring so no piece displaces its own rows
+        for (int done = 0; done < n;) {
+            const int p = pos0 + done, m = std::min(n - done, rc_);
+            spill_to(s, layer, std::min(p, p + m - rc_));
+            MKKV_CK(launch_append(s.views[layer], k + (size_t) done * NKV * HD, v + (size_t) done * NKV * HD, p, m, stream_));
+            done += m;
+        }
+    } else {
+        MKKV_CK(launch_append(s.views[layer], k, v, pos0, n, stream_));
+    }
+    s.kv_top = std::max(s.kv_top, pos0 + n);
+}
+
+void KvEngine::ensure_work(int items, int njobs) {
+    if (items > work_items_) {
+        MKKV_CK(cudaStreamSynchronize(stream_));
+        cudaFree(part_);
+        cudaFree(ml_);
+        part_ = nullptr;
+        ml_ = nullptr;
+        MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&part_), (size_t) items * AR * HD * sizeof(float)));
+        MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&ml_), (size_t) items * AR * sizeof(float2)));
+        work_items_ = items;
+    }
+    if (njobs > work_jobs_) {
+        MKKV_CK(cudaStreamSynchronize(stream_));
+        cudaFree(d_jobs_);
+        cudaFreeHost(h_jobs_);
+        cudaFree(d_ajobs_);
+        cudaFreeHost(h_ajobs_);
+        d_jobs_ = nullptr;
+        h_jobs_ = nullptr;
+        d_ajobs_ = nullptr;
+        h_ajobs_ = nullptr;
+        MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&d_jobs_), sizeof(AttnJob) * njobs));
+        MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&h_jobs_), sizeof(AttnJob) * njobs, cudaHostAllocDefault));
+        MKKV_CK(cudaMalloc(&d_ajobs_, sizeof(AppendJob) * njobs));
+        MKKV_CK(cudaHostAlloc(&h_ajobs_, sizeof(AppendJob) * njobs, cudaHostAllocDefault));
+        work_jobs_ = njobs;
+    }
+}
+void KvEngine::reserve_batch(int njobs) {
+    use_device();
+    if (njobs < 1 || njobs > 4096) throw std::runtime_error("reserve_batch: njobs out of range");
+    ensure_work(njobs * NKV * ATT_NCH, njobs);
+}
+
+void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O) {
+    use_device();
+    check_layer(layer);
+    Seq & s = seq_ref(seq);
+    if (T < 1 || T > MAXT) throw std::runtime_error("attend: T must be 1.." + std::to_string(MAXT));
+    if (n < 0 || n + T > s.kv_top) throw std::runtime_error("attend: rows up to " + std::to_string(n + T) + " have not been appended (" + std::to_string(s.kv_top) + " written)");
+    if (!Q || !O) throw std::runtime_error("attend: null Q / O");
+    wait_copies(s);
+    AttnJob j;
+    j.kv = s.views[layer];
+    j.Q = static_cast<const uint16_t *>(Q);
+    j.O = static_cast<float *>(O);
+    j.n = n;
+    j.T = T;
+    attn_dims(n + T, j.nch, j.cs);
+    j.ws = kv_ws(n + T, cfg_.win);
+    j.item0 = 0;
+    spill_to(s, layer, j.ws); // positions that left the window are read in the main format from now on
+    MKKV_CK(launch_attend(nullptr, &j, 1, NKV * j.nch, T, part_, ml_, d_status_, stream_));
+}
+
+void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n, const int * T, const void * K, const void * V, const void * Q,
+                          void * O, bool do_append) {
+    use_device();
+    check_layer(layer);
+    if (njobs < 1) return;
+    if (njobs > work_jobs_) throw std::runtime_error("step_batch: call reserve_batch(" + std::to_string(njobs) + ") first");
+    // the job tables are reused by every call: the previous call's upload must have been consumed
+    MKKV_CK(cudaEventSynchronize(ev_compute_));
+    AppendJob * aj = static_cast<AppendJob *>(h_ajobs_);
+    int items = 0, maxT = 0;
+    size_t row = 0;
+    for (int j = 0; j < njobs; j++) {
+        Seq & s = seq_ref(seqs[j]);
+        for (int k = 0; k < j; k++)
+            if (seqs[k] == seqs[j]) throw std::runtime_error("step_batch: sequence listed twice");
+        if (T[j] < 1 || T[j] > MAXT) throw std::runtime_error("step_batch: T must be 1.." + std::to_string(MAXT));
+        if (n[j] < 0 || n[j] + T[j] > (do_append ? s.ctx : s.kv_top)) throw std::runtime_error("step_batch: rows out of range for job " + std::to_string(j));
+        wait_copies(s);
+        if (do_append && cfg_.spill && rc_ > 0) spill_to(s, layer, n[j] + T[j] - rc_);
+        AttnJob & a = h_jobs_[j];
+        a.kv = s.views[layer];
+        a.Q = static_cast<const uint16_t *>(Q) + row * NH * HD;
+        a.O = static_cast<float *>(O) + row * NH * HD;
+        a.n = n[j];
+        a.T = T[j];
+        attn_dims(n[j] + T[j], a.nch, a.cs);
+        a.ws = kv_ws(n[j] + T[j], cfg_.win);
+        a.item0 = items;
+        items += NKV * a.nch;
+        maxT = std::max(maxT, T[j]);
+        aj[j].kv = a.kv;
+        aj[j].K = static_cast<const uint16_t *>(K) + row * NKV * HD;
+        aj[j].V = static_cast<const uint16_t *>(V) + row * NKV * HD;
+        aj[j].pos0 = n[j];
+        aj[j].n = T[j];
+        row += T[j];
+        spill_to(s, layer, a.ws);
+        if (do_append) s.kv_top = std::max(s.kv_top, n[j] + T[j]);
+    }
+    if (items > work_items_) throw std::runtime_error("step_batch: call reserve_batch first");
+    if (do_append) {
+        MKKV_CK(cudaMemcpyAsync(d_ajobs_, h_ajobs_, sizeof(AppendJob) * njobs, cudaMemcpyHostToDevice, stream_));
+        MKKV_CK(launch_append_batch(static_cast<const AppendJob *>(d_ajobs_), njobs, maxT, stream_));
+    }
+    MKKV_CK(cudaMemcpyAsync(d_jobs_, h_jobs_, sizeof(AttnJob) * njobs, cudaMemcpyHostToDevice, stream_));
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(launch_attend(d_jobs_, h_jobs_, njobs, items, maxT, part_, ml_, d_status_, stream_));
+}
+
+// ---- rewind ----
+
+// ring rows of positions that the abandoned continuation overwrote are rebuilt from the main rows (ck_pool.cu:285-296)
+void KvEngine::ring_rewind(Seq & s, int P) {
+    if (cfg_.win > 0) {
+        const int p0 = std::max(0, P - rc_), p1 = std::min(P, s.kv_top - rc_);
+        if (p1 > p0) MKKV_CK(launch_refill(s.d_views, cfg_.layers, p0, p1, stream_));
+    }
+    s.kv_top = std::min(s.kv_top, P);
+    for (int & sp : s.spilled) sp = std::min(sp, P);
+}
+
+void KvEngine::truncate(int seq, int len) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    if (len < 0 || len > s.n) throw std::runtime_error("truncate: length " + std::to_string(len) + " not inside the sequence (" + std::to_string(s.n) + ")");
+    wait_copies(s);
+    ring_rewind(s, len);
+    s.n = len;
+    drop_checkpoints(s, len);
+}
+
+size_t KvEngine::ring_state_bytes() const {
+    size_t nring = 0;
+    for (int w = 0; w < 2; w++)
+        for (int l = 0; l < cfg_.layers; l++) nring += ring_[w][l];
+    return nring * NKV * rc_ * (HD + SCALE_ROW);
+}
+
+int KvEngine::checkpoint(int seq) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    const int pos = s.n;
+    for (auto & k : s.cks)
+        if (k.pos == pos) return pos;
+    int max_slots = 8;
+    if (const char * c = getenv("MK_CK_SLOTS")) max_slots = std::max(1, atoi(c));
+    if ((int) s.cks.size() >= max_slots) { // the oldest goes (the reference thins by coverage; any policy keeps rewinds exact)
+        if (s.cks.front().ring) cudaFreeHost(s.cks.front().ring);
+        s.cks.erase(s.cks.begin());
+    }
+    Checkpoint k;
+    k.pos = pos;
+    const size_t rb = ring_state_bytes();
+    if (cfg_.exact && rb) { // the rings as of pos, so a rewind restores them exactly (ck_pool.cu:135-158)
+        MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&k.ring), rb, cudaHostAllocDefault));
+        const size_t vbytes = rb / (HD + SCALE_ROW) * HD;
+        wait_copies(s);
+        MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+        MKKV_CK(cudaStreamWaitEvent(st_copy_, ev_compute_, 0));
+        MKKV_CK(cudaMemcpyAsync(k.ring, s.ring_val, vbytes, cudaMemcpyDeviceToHost, st_copy_));
+        MKKV_CK(cudaMemcpyAsync(k.ring + vbytes, s.ring_sc, rb - vbytes, cudaMemcpyDeviceToHost, st_copy_));
+        MKKV_CK(cudaEventRecord(s.copy_done, st_copy_));
+        s.copy_pending = true; // the next launch that writes ring rows waits for the copy
+        k.ring_ok = true;
+    }
+    s.cks.push_back(k);
+    std::sort(s.cks.begin(), s.cks.end(), [](const Checkpoint & a, const Checkpoint & b) { return a.pos < b.pos; });
+    return pos;
+}
+
+std::vector<int> KvEngine::checkpoints(int seq) const {
+    std::vector<int> v;
+    for (const auto & k : seq_ref(seq).cks) v.push_back(k.pos);
+    return v;
+}
+
+bool KvEngine::rewind_to(int seq, int pos) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    const Checkpoint * ck = nullptr;
+    for (const auto & k : s.cks)
+        if (k.pos == pos && pos >= 0) ck = &k;
+    if (!ck) return false;
+    wait_copies(s);
+    if (ck->ring_ok) { // exact mode: the rings go back to their state at pos (ck_pool.cu:208-214,279)
+        const size_t rb = ring_state_bytes(), vbytes = rb / (HD + SCALE_ROW) * HD;
+        MKKV_CK(cudaMemcpyAsync(s.ring_val, ck->ring, vbytes, cudaMemcpyHostToDevice, stream_));
+        MKKV_CK(cudaMemcpyAsync(s.ring_sc, ck->ring + vbytes, rb - vbytes, cudaMemcpyHostToDevice, stream_));
+        s.kv_top = std::min(s.kv_top, pos);
+        for (int & sp : s.spilled) sp = std::min(sp, pos);
+    } else {
+        ring_rewind(s, pos);
+    }
+    s.n = pos;
+    drop_checkpoints(s, pos);
+    return true;
+}
+
+// ---- host store ----
+
+char * KvEngine::hs_new() {
+    if (hs_alloc_ + hs_chunk_ > hs_budget_) return nullptr;
+    char * c = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void **>(&c), hs_chunk_, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    hs_alloc_ += hs_chunk_;
+    return c;
+}
+char * KvEngine::hs_take() {
+    if (!hs_free_.empty()) {
+        char * c = hs_free_.back();
+        hs_free_.pop_back();
+        return c;
+    }
+    return hs_new();
+}
+void KvEngine::hs_trim() {
+    while (hs_alloc_ > hs_budget_ && !hs_free_.empty()) {
+        cudaFreeHost(hs_free_.back());
+        hs_free_.pop_back();
+        hs_alloc_ -= hs_chunk_;
+    }
+}
+void KvEngine::hs_release(Blob & b) {
+    for (char * c : b.chunks) hs_free_.push_back(c);
+    b = Blob();
+    hs_trim();
+}
+// chunks for `bytes` more bytes of b; false: the budget is spent (b keeps what it has)
+bool KvEngine::blob_room(Blob & b, size_t bytes) {
+    const size_t need = (b.used + bytes + hs_chunk_ - 1) / hs_chunk_;
+    while (b.chunks.size() < need) {
+        char * c = hs_take();
+        if (!c) return false;
+        b.chunks.push_back(c);
+    }
+    return true;
+}
+size_t KvEngine::hs_used() const {
+    size_t n = sw_blob_.chunks.size();
+    for (const auto & p : parked_) n += p.second.blob.chunks.size();
+    return n * hs_chunk_;
+}
+void KvEngine::store_budget(size_t bytes) {
+    use_device();
+    hs_budget_ = bytes;
+    hs_trim();
+}
+void KvEngine::store_reserve(size_t bytes) {
+    use_device();
+    size_t free_b = hs_free_.size() * hs_chunk_;
+    while (free_b < bytes) {
+        char * c = hs_new();
+        if (!c) break;
+        hs_free_.push_back(c);
+        free_b += hs_chunk_;
+    }
+}
+KvEngine::StoreInfo KvEngine::store_info() const {
+    StoreInfo i;
+    i.budget = hs_budget_;
+    i.allocated = hs_alloc_;
+    i.used = hs_used();
+    i.parked = (int) parked_.size();
+    i.last_ms = hs_ms_;
+    i.last_bytes = hs_bytes_;
+    i.side_ms = sw_ms_;
+    return i;
+}
+void KvEngine::kv_sizes(size_t * per_token, size_t * rings, size_t * state, size_t * checkpoint) const {
+    size_t t = 0;
+    for (int l = 0; l < cfg_.layers; l++)
+        for (int w = 0; w < 2; w++) t += (size_t) NKV * (row_bytes(kvb_[w][l]) + SCALE_ROW);
+    *per_token = t;
+    *rings = ring_state_bytes();
+    *state = 0; // no recurrent state on this path
+    *checkpoint = cfg_.exact ? ring_state_bytes() : 0;
+}
+
+void KvEngine::ensure_staging() {
+    if (!staging_) MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&staging_), 2 * hs_chunk_));
+}
+
+size_t KvEngine::stream_bytes(const Seq & s, int a, int b, int ra, int rb) const {
+    size_t t = 0;
+    for (const auto & r : s.regions) t += (size_t) r.row_bytes * (size_t) std::max(0, r.ring ? rb - ra : b - a);
+    return t;
+}
+
+void KvEngine::run_copy(Seq & s, int a, int b, int ra, int rb, Blob & blob, size_t blob_off, bool to_host) {
+    ensure_staging();
+    const size_t total = stream_bytes(s, a, b, ra, rb);
+    int k = 0;
+    for (size_t off = 0; off < total; k++) {
+        const size_t bpos = blob_off + off, ci = bpos / hs_chunk_, co = bpos % hs_chunk_;
+        const size_t len = std::min(total - off, hs_chunk_ - co);
+        uint8_t * stage = staging_ + (size_t) (k & 1) * hs_chunk_;
+        if (to_host) {
+            MKKV_CK(launch_gather(s.d_regions, (int) s.regions.size(), a, b, ra, rb, off, len, stage, false, st_copy_));
+            MKKV_CK(cudaMemcpyAsync(blob.chunks[ci] + co, stage, len, cudaMemcpyDeviceToHost, st_copy_));
+        } else {
+            MKKV_CK(cudaMemcpyAsync(stage, blob.chunks[ci] + co, len, cudaMemcpyHostToDevice, st_copy_));
+            MKKV_CK(launch_gather(s.d_regions, (int) s.regions.size(), a, b, ra, rb, off, len, stage, true, st_copy_));
+        }
+        off += len;
+    }
+}
+
+void KvEngine::store_wait() {
+    use_device();
+    MKKV_CK(cudaStreamSynchronize(st_copy_));
+    copies_in_flight_ = false;
+}
+
+size_t KvEngine::park_need(int seq, int max_checkpoints) const {
+    const Seq & s = seq_ref(seq);
+    size_t t = stream_bytes(s, 0, s.n, 0, rc_);
+    int k = 0;
+    for (auto it = s.cks.rbegin(); it != s.cks.rend() && k < max_checkpoints; ++it, ++k)
+        if (it->ring_ok) t += ring_state_bytes();
+    return t;
+}
+size_t KvEngine::park_bytes(int id) const {
+    const auto it = parked_.find(id);
+    return it == parked_.end() ? 0 : it->second.blob.used;
+}
+int KvEngine::park_len(int id) const {
+    const auto it = parked_.find(id);
+    return it == parked_.end() ? -1 : it->second.n;
+}
+
+int KvEngine::park(int seq, int max_checkpoints, bool wait) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    if (s.n == 0) return 0;
+    const auto t0 = std::chrono::steady_clock::now();
+    // spill mode: every position of the sequence gets its main-format row first, so the entry is the reference's byte
+    // stream (host_store.cu:243-265) and needs no fp16 shadow
+    for (int l = 0; l < cfg_.layers; l++) spill_to(s, l, s.n);
+    Parked e;
+    e.n = s.n;
+    e.kv_top = s.n;
+    e.ctxp = s.ctxp;
+    e.kv_bytes = stream_bytes(s, 0, s.n, 0, 0);
+    e.ring_bytes = stream_bytes(s, 0, 0, 0, rc_);
+    size_t need = e.kv_bytes + e.ring_bytes;
+    std::vector<const Checkpoint *> keep;
+    for (auto it = s.cks.rbegin(); it != s.cks.rend() && (int) keep.size() < max_checkpoints; ++it) keep.push_back(&*it);
+    for (const Checkpoint * k : keep)
+        if (k->ring_ok) need += ring_state_bytes();
+    if (!blob_room(e.blob, need)) {
+        hs_release(e.blob);
+        return -1;
+    }
+    wait_copies(s);
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(cudaStreamWaitEvent(st_copy_, ev_compute_, 0));
+    run_copy(s, 0, s.n, 0, rc_, e.blob, 0, true);
+    MKKV_CK(cudaEventRecord(s.copy_done, st_copy_));
+    s.copy_pending = true; // later launches on this sequence wait until the rows and rings are out
+    e.blob.used = e.kv_bytes + e.ring_bytes;
+    if (!keep.empty()) MKKV_CK(cudaStreamSynchronize(st_copy_)); // (a checkpoint's ring copy may still be in flight)
+    for (const Checkpoint * k : keep) {
+        Checkpoint c;
+        c.pos = k->pos;
+        c.ring_ok = k->ring_ok;
+        e.cks.push_back(c);
+        e.ck_off.push_back(e.blob.used);
+        if (k->ring_ok) { // host item: memcpy over the chunk borders
+            const size_t rb = ring_state_bytes();
+            for (size_t done = 0; done < rb;) {
+                const size_t bp = e.blob.used, ci = bp / hs_chunk_, co = bp % hs_chunk_, len = std::min(rb - done, hs_chunk_ - co);
+                memcpy(e.blob.chunks[ci] + co, k->ring + done, len);
+                done += len;
+                e.blob.used += len;
+            }
+        }
+    }
+    copies_in_flight_ = true;
+    if (wait) store_wait();
+    const int id = park_next_++;
+    hs_bytes_ = e.blob.used;
+    hs_ms_ = ms_since(t0);
+    parked_.emplace(id, std::move(e));
+    return id;
+}
+
+bool KvEngine::unpark(int seq, int id, bool wait) {
+    use_device();
+    const auto it = parked_.find(id);
+    if (it == parked_.end()) return false;
+    Seq & s = seq_ref(seq);
+    Parked & e = it->second;
+    if (e.n > s.ctx) throw std::runtime_error("unpark: the parked conversation (" + std::to_string(e.n) + " positions) does not fit the sequence's context");
+    const auto t0 = std::chrono::steady_clock::now();
+    if (seq == SEQ_MAIN && sw_on_) throw std::runtime_error("unpark: a side request is active");
+    reset(seq);
+    // the side stream starts after the compute stream's pending work on this sequence
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(cudaStreamWaitEvent(st_copy_, ev_compute_, 0));
+    run_copy(s, 0, e.n, 0, rc_, e.blob, 0, false);
+    MKKV_CK(cudaEventRecord(s.copy_done, st_copy_));
+    s.copy_pending = true;
+    MKKV_CK(cudaStreamSynchronize(st_copy_)); // the chunks go back to the free list below
+    for (size_t i = 0; i < e.cks.size(); i++) {
+        Checkpoint c = e.cks[i];
+        if (c.ring_ok) {
+            const size_t rb = ring_state_bytes();
+            MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&c.ring), rb, cudaHostAllocDefault));
+            size_t bp = e.ck_off[i];
+            for (size_t done = 0; done < rb;) {
+                const size_t ci = bp / hs_chunk_, co = bp % hs_chunk_, len = std::min(rb - done, hs_chunk_ - co);
+                memcpy(c.ring + done, e.blob.chunks[ci] + co, len);
+                done += len;
+                bp += len;
+            }
+        }
+        s.cks.push_back(c);
+    }
+    std::sort(s.cks.begin(), s.cks.end(), [](const Checkpoint & a, const Checkpoint & b) { return a.pos < b.pos; });
+    s.n = e.n;
+    s.kv_top = e.n;
+    std::fill(s.spilled.begin(), s.spilled.end(), e.n);
+    hs_bytes_ = e.blob.used;
+    hs_release(e.blob);
+    parked_.erase(it);
+    (void) wait;
+    hs_ms_ = ms_since(t0);
+    return true;
+}
+
+// Rows [0, P) of a parked conversation into the sequence, leaving the entry parked: the main rows of every region come
+// straight from the pinned entry (one copy per region and chunk crossing), the window rings of the P positions are rebuilt
+// from the main rows as a rewind does (ck_pool.cu:285-296 with every ring row stale).
+bool KvEngine::restore_prefix(int seq, int id, int P, bool wait) {
+    use_device();
+    const auto it = parked_.find(id);
+    if (it == parked_.end()) return false;
+    Seq & s = seq_ref(seq);
+    const Parked & e = it->second;
+    if (P < 0 || P > e.n || P > s.ctx) throw std::runtime_error("restore_prefix: position " + std::to_string(P) + " outside the parked conversation");
+    const auto t0 = std::chrono::steady_clock::now();
+    reset(seq);
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(cudaStreamWaitEvent(st_copy_, ev_compute_, 0));
+    size_t off = 0, moved = 0;
+    for (const auto & r : s.regions) {
+        if (r.ring) break;
+        const size_t want = (size_t) P * r.row_bytes;
+        for (size_t done = 0; done < want;) {
+            const size_t bp = off + done, ci = bp / hs_chunk_, co = bp % hs_chunk_, len = std::min(want - done, hs_chunk_ - co);
+            MKKV_CK(cudaMemcpyAsync(r.base + done, e.blob.chunks[ci] + co, len, cudaMemcpyHostToDevice, st_copy_));
+            done += len;
+        }
+        moved += want;
+        off += (size_t) e.n * r.row_bytes;
+    }
+    if (cfg_.win > 0 && P > 0) MKKV_CK(launch_refill(s.d_views, cfg_.layers, std::max(0, P - rc_), P, st_copy_));
+    MKKV_CK(cudaEventRecord(s.copy_done, st_copy_));
+    s.copy_pending = true;
+    copies_in_flight_ = true;
+    s.n = P;
+    s.kv_top = P;
+    std::fill(s.spilled.begin(), s.spilled.end(), P);
+    for (const auto & c : e.cks)
+        if (c.pos <= P && !c.ring_ok) s.cks.push_back(c);
+    if (wait) store_wait();
+    hs_bytes_ = moved;
+    hs_ms_ = ms_since(t0);
+    return true;
+}
+
+bool KvEngine::park_drop(int id) {
+    const auto it = parked_.find(id);
+    if (it == parked_.end()) return false;
+    use_device();
+    MKKV_CK(cudaStreamSynchronize(st_copy_));
+    hs_release(it->second.blob);
+    parked_.erase(it);
+    return true;
+}
+
+// ---- side request: the main sequence kept aside while a short unrelated one runs (host_store.cu:186-206,297-355) ----
+
+bool KvEngine::side_begin() {
+    use_device();
+    if (sw_on_) throw std::runtime_error("side_begin: a side request is already active");
+    if (hs_budget_ == 0) return false;
+    Seq & s = main_;
+    for (int l = 0; l < cfg_.layers; l++) spill_to(s, l, s.n); // (the shadow rows will be overwritten: make the main rows now)
+    sw_on_ = true;
+    sw_broken_ = false;
+    sw_n_ = s.n;
+    sw_top_ = s.n;
+    sw_hi_ = 0;
+    sw_rings_saved_ = false;
+    sw_spilled_ = s.spilled;
+    sw_cks_ = std::move(s.cks);
+    s.cks.clear();
+    sw_pieces_.clear();
+    sw_ms_ = 0;
+    s.n = s.kv_top = 0;
+    std::fill(s.spilled.begin(), s.spilled.end(), 0);
+    return true;
+}
+
+// rows below X of the main buffers (and, once, the rings) are about to be overwritten by the side request: copy the kept
+// sequence's rows [sw_hi, up) out first, 1024 rows at a time (host_store.cu:186-206)
+void KvEngine::sw_need(int X) {
+    if (!sw_on_ || sw_broken_) return;
+    constexpr int SW_BLK = 1024;
+    const int up = (X + MAXT + SW_BLK - 1) / SW_BLK * SW_BLK;
+    const int want = std::max(sw_hi_, std::min(sw_top_, up));
+    const bool rings = !sw_rings_saved_ && rc_ > 0;
+    if (want <= sw_hi_ && !rings) return;
+    const auto t0 = std::chrono::steady_clock::now();
+    Seq & s = main_;
+    const int ra = 0, rb = rings ? rc_ : 0;
+    const size_t bytes = stream_bytes(s, sw_hi_, want, ra, rb);
+    if (!blob_room(sw_blob_, bytes)) {
+        sw_broken_ = true;
+        fprintf(stderr, "[mk] side request: the host store is full at row %d: the kept sequence is dropped\n", X);
+        return;
+    }
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(cudaStreamWaitEvent(st_copy_, ev_compute_, 0));
+    run_copy(s, sw_hi_, want, ra, rb, sw_blob_, sw_blob_.used, true);
+    sw_pieces_.push_back({sw_hi_, want, rings, sw_blob_.used, bytes});
+    sw_blob_.used += bytes;
+    MKKV_CK(cudaStreamSynchronize(st_copy_)); // the launch that overwrites the rows comes next
+    sw_hi_ = want;
+    if (rings) sw_rings_saved_ = true;
+    sw_ms_ += ms_since(t0);
+}
+
+int KvEngine::side_end() {
+    use_device();
+    if (!sw_on_) throw std::runtime_error("side_end: no side request");
+    const auto t0 = std::chrono::steady_clock::now();
+    Seq & s = main_;
+    reset(SEQ_MAIN);
+    if (sw_broken_) {
+        side_drop();
+        return 0;
+    }
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(cudaStreamWaitEvent(st_copy_, ev_compute_, 0));
+    size_t moved = 0;
+    for (const auto & p : sw_pieces_) {
+        run_copy(s, p.a, p.b, 0, p.rings ? rc_ : 0, sw_blob_, p.off, false);
+        moved += p.bytes;
+    }
+    MKKV_CK(cudaStreamSynchronize(st_copy_));
+    s.n = sw_n_;
+    s.kv_top = sw_top_;
+    s.spilled = sw_spilled_;
+    s.cks = std::move(sw_cks_);
+    sw_cks_.clear();
+    sw_on_ = false;
+    sw_pieces_.clear();
+    hs_bytes_ = moved;
+    hs_release(sw_blob_);
+    hs_ms_ = ms_since(t0);
+    return 1;
+}
+
+void KvEngine::side_drop() {
+    use_device();
+    MKKV_CK(cudaStreamSynchronize(st_copy_));
+    sw_on_ = false;
+    sw_pieces_.clear();
+    for (auto & k : sw_cks_)
+        if (k.ring) cudaFreeHost(k.ring);
+    sw_cks_.clear();
+    hs_release(sw_blob_);
+    reset(SEQ_MAIN);
+}
+
+// ---- test helpers ----
+
+static unsigned long long dg_hash(const void * p, size_t nb, unsigned long long h = 0xcbf29ce484222325ULL) {
+    const unsigned char * b = static_cast<const unsigned char *>(p);
+    size_t i = 0;
+    for (; i + 8 <= nb; i += 8) {
+        unsigned long long w;
+        memcpy(&w, b + i, 8);
+        h = (h ^ w) * 0x100000001b3ULL;
+        h ^= h >> 31;
+    }
+    for (; i < nb; i++) h = (h ^ b[i]) * 0x100000001b3ULL;
+    return h;
+}
+
+// Header of 8 words, then per (layer, side, kv head, position < n) the hash of its main row (values then scales), then per
+// (layer, side, kv head, position in [ring_lo, n)) the hash of its ring row, 0 for a side without a ring (engine.cu:1438-1500).
+// Words 2 and 7 of the reference's header describe state outside this path and are 0.
+std::vector<unsigned long long> KvEngine::state_digest(int seq) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    sync();
+    typedef unsigned long long u64;
+    const int n = s.n, rc = cfg_.win > 0 ? rc_ : 0, rlo = rc ? std::max(0, n - rc) : n;
+    std::vector<u64> out = {0x4d4b444701ULL, (u64) n, 0, (u64) rc, (u64) rlo, (u64) cfg_.layers, (u64) NKV, 0};
+    std::vector<unsigned char> vb, sb;
+    auto d2h = [&](std::vector<unsigned char> & dst, const void * src, size_t nb) {
+        dst.resize(std::max<size_t>(1, nb));
+        if (nb) MKKV_CK(cudaMemcpy(dst.data(), src, nb, cudaMemcpyDeviceToHost));
+    };
+    for (int l = 0; l < cfg_.layers; l++)
+        for (int w = 0; w < 2; w++)
+            for (int g = 0; g < NKV; g++) {
+                const KvSide & sd = s.views[l].s[w];
+                const size_t rb = row_bytes(sd.bits);
+                d2h(vb, sd.val + (size_t) g * s.ctxp * rb, n * rb);
+                d2h(sb, sd.sc + (size_t) g * s.ctxp * 8, (size_t) n * SCALE_ROW);
+                for (int p = 0; p < n; p++) out.push_back(dg_hash(sb.data() + (size_t) p * SCALE_ROW, SCALE_ROW, dg_hash(vb.data() + p * rb, rb)));
+            }
+    for (int l = 0; l < cfg_.layers; l++)
+        for (int w = 0; w < 2; w++)
+            for (int g = 0; g < NKV; g++) {
+                const KvSide & sd = s.views[l].s[w];
+                if (!rc || !sd.rval) {
+                    out.insert(out.end(), n - rlo, 0ULL);
+                    continue;
+                }
+                d2h(vb, sd.rval + (size_t) g * rc * HD, (size_t) rc * HD);
+                d2h(sb, sd.rsc + (size_t) g * rc * 8, (size_t) rc * SCALE_ROW);
+                for (int p = rlo; p < n; p++) {
+                    const size_t r = p % rc;
+                    out.push_back(dg_hash(sb.data() + r * SCALE_ROW, SCALE_ROW, dg_hash(vb.data() + r * HD, HD)));
+                }
+            }
+    return out;
+}
+
+int KvEngine::read_row(int seq, int layer, int side, int g, int pos, bool ring, void * val, void * sc) {
+    use_device();
+    check_layer(layer);
+    Seq & s = seq_ref(seq);
+    if (side < 0 || side > 1 || g < 0 || g >= NKV) throw std::runtime_error("read_row: bad side / kv head");
+    const KvSide & sd = s.views[layer].s[side];
+    sync();
+    if (ring) {
+        if (!sd.rval || pos < 0 || pos >= rc_) throw std::runtime_error("read_row: no such ring row");
+        MKKV_CK(cudaMemcpy(val, sd.rval + ((size_t) g * rc_ + pos) * HD, HD, cudaMemcpyDeviceToHost));
+        MKKV_CK(cudaMemcpy(sc, sd.rsc + ((size_t) g * rc_ + pos) * 8, SCALE_ROW, cudaMemcpyDeviceToHost));
+        return HD;
+    }
+    if (pos < 0 || pos >= s.ctxp) throw std::runtime_error("read_row: position out of range");
+    const size_t rb = row_bytes(sd.bits);
+    MKKV_CK(cudaMemcpy(val, sd.val + ((size_t) g * s.ctxp + pos) * rb, rb, cudaMemcpyDeviceToHost));
+    MKKV_CK(cudaMemcpy(sc, sd.sc + ((size_t) g * s.ctxp + pos) * 8, SCALE_ROW, cudaMemcpyDeviceToHost));
+    return (int) rb;
+}
+
+void KvEngine::write_row(int seq, int layer, int side, int g, int pos, bool ring, const void * val, const void * sc) {
+    use_device();
+    check_layer(layer);
+    Seq & s = seq_ref(seq);
+    if (side < 0 || side > 1 || g < 0 || g >= NKV) throw std::runtime_error("write_row: bad side / kv head");
+    const KvSide & sd = s.views[layer].s[side];
+    sync();
+    if (ring) {
+        if (!sd.rval || pos < 0 || pos >= rc_) throw std::runtime_error("write_row: no such ring row");
+        MKKV_CK(cudaMemcpy(sd.rval + ((size_t) g * rc_ + pos) * HD, val, HD, cudaMemcpyHostToDevice));
+        MKKV_CK(cudaMemcpy(sd.rsc + ((size_t) g * rc_ + pos) * 8, sc, SCALE_ROW, cudaMemcpyHostToDevice));
+        return;
+    }
+    if (pos < 0 || pos >= s.ctxp) throw std::runtime_error("write_row: position out of range");
+    const size_t rb = row_bytes(sd.bits);
+    MKKV_CK(cudaMemcpy(sd.val + ((size_t) g * s.ctxp + pos) * rb, val, rb, cudaMemcpyHostToDevice));
+    MKKV_CK(cudaMemcpy(sd.sc + ((size_t) g * s.ctxp + pos) * 8, sc, SCALE_ROW, cudaMemcpyHostToDevice));
+    s.kv_top = std::max(s.kv_top, pos + 1);
+}
+
+} // namespace mkkv

@@ -1,0 +1,51 @@
+// Host-callable launchers of the KV hot-path kernels (sm_100a). Every launcher enqueues on `stream` and returns the
+// launch's cudaError_t; none allocates or synchronises.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "kv_format.h"
+
+namespace mkkv {
+
+// error word values a kernel may leave in the engine's mapped status word
+enum KernelStatus : int { KS_OK = 0, KS_WAIT_TIMEOUT = 1 };
+
+// rows pos0 .. pos0 + n - 1 of one (sequence, layer): K, V fp16 [n][4][256] -> ring q8 row (+ fp16 shadow) and, in eager
+// mode or for a side without a ring, the main-format row
+cudaError_t launch_append(const KvView & kv, const uint16_t * K, const uint16_t * V, int pos0, int n, cudaStream_t stream);
+// spill mode: main-format rows of positions [p0, p1) of the layers' ring sides, quantized from the fp16 shadow.
+// views: device array of KvView, one per layer
+cudaError_t launch_spill(const KvView * views, int layers, int p0, int p1, cudaStream_t stream);
+// ring rows of positions [p0, p1) rebuilt from the main rows (after a rewind), all layers of one sequence
+cudaError_t launch_refill(const KvView * views, int layers, int p0, int p1, cudaStream_t stream);
+
+// split-K decode attention over the (kv head, chunk) items of njobs jobs, then the merge. jobs: device array (njobs > 1)
+// or null with the single job passed by value. part: [items][48][256] fp32, ml: [items][48] (m, l). status: device-visible word.
+cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
+                          float2 * ml, int * status, cudaStream_t stream);
+
+// batched append: job j writes n rows at pos0 of its own (sequence, layer)
+struct AppendJob {
+    KvView kv;
+    const uint16_t * K;
+    const uint16_t * V;
+    int pos0, n;
+};
+cudaError_t launch_append_batch(const AppendJob * jobs_dev, int njobs, int max_n, cudaStream_t stream);
+
+// Snapshot gather / restore scatter between the cache regions of one sequence and a contiguous staging buffer.
+// The snapshot byte stream is, region after region, rows [a, b) of every main region and ring rows [ra, rb) of every ring
+// region (host_store.cu:77-107 order: layer, side, kv head: values, scales; then the rings). This launch moves stream bytes
+// [off, off + len) to / from staging[0 .. len). Row sizes are multiples of 16 bytes, so are off and len.
+struct CopyRegion {
+    uint8_t * base;     // first row of the region (one kv head's values or scales, main or ring)
+    unsigned row_bytes; // bytes per row
+    unsigned ring;      // 1: indexed by ring row, 0: by position
+};
+constexpr int MAX_REGIONS = MAX_LAYERS * 2 * NKV * 2 * 2;
+cudaError_t launch_gather(const CopyRegion * regions, int nregions, int a, int b, int ra, int rb, unsigned long long off,
+                          unsigned long long len, uint8_t * staging, bool scatter, cudaStream_t stream);
+
+size_t attend_smem_bytes();
+
+} // namespace mkkv

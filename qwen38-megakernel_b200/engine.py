@@ -1,0 +1,314 @@
+"""ctypes binding of the KV hot path's C ABI (include/mk_kv.h), in the style of the reference's server/mk_engine.py.
+
+Tensor arguments are device pointers: pass torch CUDA tensors (their data_ptr is used) or plain integers.
+"""
+import ctypes as C
+import json
+import os
+
+NH, NKV, HD, MAXT = 24, 4, 256, 8
+SEQ_MAIN = -1
+FLAG_SPILL, FLAG_WIN_ALL, FLAG_EXACT = 1, 2, 4
+
+_DIR = os.path.dirname(os.path.abspath(__file__))
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+def lib_path():
+    return os.environ.get("MK_KV_LIB", os.path.join(_DIR, "libmk_kv.so"))
+
+
+_lib = None
+
+
+def load_library():
+    """Loads libmk_kv.so and declares every export of include/mk_kv.h. Raises if the library has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        raise EngineError("libmk_kv.so is not built (%s): run __graft_entry__.build() or make -C %s/csrc" % (path, _DIR))
+    L = C.CDLL(path)
+    vp, i, ll, cp = C.c_void_p, C.c_int, C.c_longlong, C.c_char_p
+    ip, llp, ullp = C.POINTER(C.c_int), C.POINTER(C.c_longlong), C.POINTER(C.c_ulonglong)
+    sig = {
+        "mk_last_error": (cp, []),
+        "mk_kv_abi_sig": (C.c_ulonglong, []),
+        "mk_build_info": (cp, []),
+        "mk_kv_new": (vp, [i, i, cp, i, i]),
+        "mk_free": (None, [vp]),
+        "mk_reset": (None, [vp]),
+        "mk_kv_set_stream": (i, [vp, vp]),
+        "mk_kv_sync": (i, [vp]),
+        "mk_kv_append": (i, [vp, i, i, i, i, vp, vp]),
+        "mk_kv_attend": (i, [vp, i, i, i, i, vp, vp]),
+        "mk_kv_step": (i, [vp, i, i, i, i, vp, vp, vp, vp]),
+        "mk_kv_reserve_batch": (i, [vp, i]),
+        "mk_kv_step_batch": (i, [vp, i, ip, i, ip, ip, vp, vp, vp, vp]),
+        "mk_kv_attend_batch": (i, [vp, i, ip, i, ip, ip, vp, vp]),
+        "mk_kv_commit": (i, [vp, i, i]),
+        "mk_kv_position": (i, [vp, i]),
+        "mk_kv_cap_T": (i, [i, i]),
+        "mk_truncate": (i, [vp, i]),
+        "mk_kv_truncate": (i, [vp, i, i]),
+        "mk_kv_checkpoint": (i, [vp, i]),
+        "mk_checkpoints": (i, [vp, ip, i]),
+        "mk_kv_checkpoints": (i, [vp, i, ip, i]),
+        "mk_rewind_to": (i, [vp, i]),
+        "mk_kv_rewind_to": (i, [vp, i, i]),
+        "mk_store_budget": (i, [vp, ll]),
+        "mk_store_reserve": (i, [vp, ll]),
+        "mk_store_info": (i, [vp, llp, i]),
+        "mk_kv_sizes": (None, [vp, llp, llp, llp, llp]),
+        "mk_park": (i, [vp, i]),
+        "mk_kv_park": (i, [vp, i, i]),
+        "mk_unpark": (i, [vp, i]),
+        "mk_kv_unpark": (i, [vp, i, i]),
+        "mk_park_drop": (i, [vp, i]),
+        "mk_park_need": (ll, [vp, i]),
+        "mk_park_bytes": (ll, [vp, i]),
+        "mk_kv_restore_prefix": (i, [vp, i, i, i, i]),
+        "mk_kv_store_wait": (i, [vp]),
+        "mk_side_begin": (i, [vp]),
+        "mk_side_end": (i, [vp]),
+        "mk_side_drop": (i, [vp]),
+        "mk_side_active": (i, [vp]),
+        "mk_slots_open": (i, [vp, i, i]),
+        "mk_slots_count": (i, [vp]),
+        "mk_state_digest": (i, [vp, ullp, i]),
+        "mk_kv_state_digest": (ll, [vp, i, ullp, ll]),
+        "mk_kv_read_row": (i, [vp, i, i, i, i, i, i, vp, vp]),
+        "mk_kv_write_row": (i, [vp, i, i, i, i, i, i, vp, vp]),
+        "mk_kv_bits": (i, [vp, i, i]),
+        "mk_kv_has_ring": (i, [vp, i, i]),
+        "mk_kv_ring_rows": (i, [vp]),
+        "mk_kv_device_bytes": (ll, [vp]),
+    }
+    for name, (res, args) in sig.items():
+        f = getattr(L, name)
+        f.restype, f.argtypes = res, args
+    L._mk_exports = sorted(sig)
+    _lib = L
+    return L
+
+
+def cap_T(n, T_req):
+    return load_library().mk_kv_cap_T(n, T_req)
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        if not x.is_cuda:
+            raise EngineError("expected a CUDA tensor")
+        if not x.is_contiguous():
+            raise EngineError("expected a contiguous tensor")
+        return x.data_ptr()
+    raise EngineError("expected a CUDA tensor or a device address")
+
+
+def _ints(v):
+    return (C.c_int * len(v))(*[int(x) for x in v])
+
+
+class Engine:
+    """One KV engine on the current CUDA device (mk_kv_new). kv_spec / kv_win take the reference's MK_KV / MK_KV_WIN."""
+
+    def __init__(self, layers, ctx, kv_spec="", kv_win=0, spill=False, win_all=False, exact=False, stream=None):
+        self.L = load_library()
+        flags = (FLAG_SPILL if spill else 0) | (FLAG_WIN_ALL if win_all else 0) | (FLAG_EXACT if exact else 0)
+        self.h = self.L.mk_kv_new(layers, ctx, kv_spec.encode(), kv_win, flags)
+        if not self.h:
+            raise EngineError(self.L.mk_last_error().decode())
+        self.layers, self.ctx = layers, ctx
+        if stream is not None:
+            self.set_stream(stream)
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.mk_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _err(self, what):
+        return EngineError("%s: %s" % (what, self.L.mk_last_error().decode()))
+
+    def _ck(self, r, what):
+        if r < 0:
+            raise self._err(what)
+        return r
+
+    # ---- plumbing ----
+    def set_stream(self, stream):
+        """stream: a torch.cuda.Stream, a raw cudaStream_t value, or 0 for the default stream."""
+        s = getattr(stream, "cuda_stream", stream)
+        self._ck(self.L.mk_kv_set_stream(self.h, s), "set_stream")
+
+    def sync(self):
+        self._ck(self.L.mk_kv_sync(self.h), "sync")
+
+    def reset(self):
+        self.L.mk_reset(self.h)
+
+    def build_info(self):
+        return json.loads(self.L.mk_build_info().decode())
+
+    # ---- hot path ----
+    def append(self, layer, pos0, K, V, seq=SEQ_MAIN):
+        n = K.shape[0] if hasattr(K, "shape") else None
+        if n is None:
+            raise EngineError("append needs tensors (use append_raw for addresses)")
+        self._ck(self.L.mk_kv_append(self.h, seq, layer, pos0, n, _ptr(K), _ptr(V)), "append")
+
+    def append_raw(self, layer, pos0, n, K, V, seq=SEQ_MAIN):
+        self._ck(self.L.mk_kv_append(self.h, seq, layer, pos0, n, _ptr(K), _ptr(V)), "append")
+
+    def attend(self, layer, n, Q, O, seq=SEQ_MAIN):
+        self._ck(self.L.mk_kv_attend(self.h, seq, layer, n, Q.shape[0], _ptr(Q), _ptr(O)), "attend")
+
+    def step(self, layer, n, K, V, Q, O, seq=SEQ_MAIN):
+        self._ck(self.L.mk_kv_step(self.h, seq, layer, n, Q.shape[0], _ptr(K), _ptr(V), _ptr(Q), _ptr(O)), "step")
+
+    def reserve_batch(self, njobs):
+        self._ck(self.L.mk_kv_reserve_batch(self.h, njobs), "reserve_batch")
+
+    def step_batch(self, seqs, layer, n, T, K, V, Q, O):
+        self._ck(self.L.mk_kv_step_batch(self.h, len(seqs), _ints(seqs), layer, _ints(n), _ints(T), _ptr(K), _ptr(V), _ptr(Q),
+                                         _ptr(O)), "step_batch")
+
+    def attend_batch(self, seqs, layer, n, T, Q, O):
+        self._ck(self.L.mk_kv_attend_batch(self.h, len(seqs), _ints(seqs), layer, _ints(n), _ints(T), _ptr(Q), _ptr(O)),
+                 "attend_batch")
+
+    def commit(self, length, seq=SEQ_MAIN):
+        self._ck(self.L.mk_kv_commit(self.h, seq, length), "commit")
+
+    def position(self, seq=SEQ_MAIN):
+        return self._ck(self.L.mk_kv_position(self.h, seq), "position")
+
+    # ---- rewind ----
+    def truncate(self, n, seq=SEQ_MAIN):
+        self._ck(self.L.mk_kv_truncate(self.h, seq, n), "truncate")
+
+    def checkpoint(self, seq=SEQ_MAIN):
+        return self._ck(self.L.mk_kv_checkpoint(self.h, seq), "checkpoint")
+
+    def checkpoints(self, seq=SEQ_MAIN):
+        n = self._ck(self.L.mk_kv_checkpoints(self.h, seq, None, 0), "checkpoints")
+        out = (C.c_int * max(n, 1))()
+        self.L.mk_kv_checkpoints(self.h, seq, out, n)
+        return list(out[:n])
+
+    def rewind_to(self, pos, seq=SEQ_MAIN):
+        return self.L.mk_kv_rewind_to(self.h, seq, pos) == 0
+
+    # ---- host store ----
+    def store_budget(self, nbytes):
+        self._ck(self.L.mk_store_budget(self.h, int(nbytes)), "store_budget")
+
+    def store_reserve(self, nbytes):
+        self._ck(self.L.mk_store_reserve(self.h, int(nbytes)), "store_reserve")
+
+    def store_info(self):
+        out = (C.c_longlong * 10)()
+        self._ck(self.L.mk_store_info(self.h, out, 10), "store_info")
+        keys = ("budget", "allocated", "used", "parked", "last_bytes", "last_us", "side_us", "kv_token_bytes", "side_park_bytes",
+                "side_park_us")
+        return dict(zip(keys, out))
+
+    def kv_sizes(self):
+        a, b, c, d = C.c_longlong(), C.c_longlong(), C.c_longlong(), C.c_longlong()
+        self.L.mk_kv_sizes(self.h, C.byref(a), C.byref(b), C.byref(c), C.byref(d))
+        return {"per_token": a.value, "rings": b.value, "state": c.value, "checkpoint": d.value}
+
+    def park(self, max_cks=0, seq=SEQ_MAIN):
+        """id > 0, 0 for an empty sequence, None when the store has no room"""
+        r = self.L.mk_kv_park(self.h, seq, max_cks)
+        if r == -3:
+            return None
+        return self._ck(r, "park")
+
+    def unpark(self, pid, seq=SEQ_MAIN):
+        self._ck(self.L.mk_kv_unpark(self.h, seq, pid), "unpark")
+
+    def park_drop(self, pid):
+        return self.L.mk_park_drop(self.h, pid) == 0
+
+    def park_need(self, max_cks=0):
+        return self.L.mk_park_need(self.h, max_cks)
+
+    def park_bytes(self, pid):
+        return self.L.mk_park_bytes(self.h, pid)
+
+    def restore_prefix(self, pid, pos, seq=SEQ_MAIN, wait=True):
+        self._ck(self.L.mk_kv_restore_prefix(self.h, seq, pid, pos, int(wait)), "restore_prefix")
+
+    def store_wait(self):
+        self._ck(self.L.mk_kv_store_wait(self.h), "store_wait")
+
+    def side_begin(self):
+        r = self._ck(self.L.mk_side_begin(self.h), "side_begin")
+        return r == 0
+
+    def side_end(self):
+        return self._ck(self.L.mk_side_end(self.h), "side_end") == 1
+
+    def side_drop(self):
+        self._ck(self.L.mk_side_drop(self.h), "side_drop")
+
+    def side_active(self):
+        return self.L.mk_side_active(self.h) == 1
+
+    # ---- slots ----
+    def slots_open(self, n, ctx=0):
+        return self._ck(self.L.mk_slots_open(self.h, n, ctx), "slots_open")
+
+    def slots_count(self):
+        return self._ck(self.L.mk_slots_count(self.h), "slots_count")
+
+    # ---- test helpers ----
+    def state_digest(self, seq=SEQ_MAIN):
+        import numpy as np
+        n = self.L.mk_kv_state_digest(self.h, seq, None, 0)
+        if n < 0:
+            raise self._err("state_digest")
+        out = np.zeros(n, dtype=np.uint64)
+        self.L.mk_kv_state_digest(self.h, seq, out.ctypes.data_as(C.POINTER(C.c_ulonglong)), n)
+        return out
+
+    def read_row(self, layer, side, g, pos, ring=False, seq=SEQ_MAIN):
+        import numpy as np
+        val = np.zeros(HD, dtype=np.uint8)
+        sc = np.zeros(8, dtype=np.uint16)
+        n = self._ck(self.L.mk_kv_read_row(self.h, seq, layer, side, g, pos, int(ring), val.ctypes.data, sc.ctypes.data), "read_row")
+        return val[:n].copy(), sc
+
+    def write_row(self, layer, side, g, pos, val, sc, ring=False, seq=SEQ_MAIN):
+        import numpy as np
+        val = np.ascontiguousarray(val, dtype=np.uint8)
+        sc = np.ascontiguousarray(sc, dtype=np.uint16)
+        self._ck(self.L.mk_kv_write_row(self.h, seq, layer, side, g, pos, int(ring), val.ctypes.data, sc.ctypes.data), "write_row")
+
+    def bits(self, side, layer):
+        return self._ck(self.L.mk_kv_bits(self.h, side, layer), "bits")
+
+    def has_ring(self, side, layer):
+        return self._ck(self.L.mk_kv_has_ring(self.h, side, layer), "has_ring") == 1
+
+    def ring_rows(self):
+        return self._ck(self.L.mk_kv_ring_rows(self.h), "ring_rows")
+
+    def device_bytes(self):
+        return self.L.mk_kv_device_bytes(self.h)
