@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache hot path: streaming decode at 101.6k positions, 16 attention layers, 8 query tokens per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step: for each of the 16 layers, append the step's K / V rows (quantize into the q8_0 ring, spill rows
+that left the window into the 5/6-bit tier) and run decode attention of 8 query tokens over the whole context; then 1..8 of
+the positions are committed. N > 1 (torchrun): every rank streams its own sequence (independent sequence slots, no
+collective). Prints one JSON line (rank 0).
+
+--impl reference times the CPU restatement of the reference's kernels (the parity oracle) on the host cores: the reference
+engine has no CPU implementation of this path, and its CUDA kernels need its whole model runtime.
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+LAYERS, CTX0, T_STEP, WIN = 16, 101600, 8, 2048
+SPEC = "K*=5r,V*=6"
+NH, NKV, HD = 24, 4, 256
+WORKLOAD = "config2: 16 attention layers, 101,600 positions, preset F layout K5r/V6 + q8_0 window 2048, 8 queries/step, streaming append+spill+attend"
+
+
+def algorithmic_bytes(n, T, kbits=5, vbits=6, win=WIN):
+    """bytes one layer's decode attention must move at context n + T: every visible row's values + scales once (q8_0 rows
+    from the window start on), Q in, O out; partials are not counted"""
+    L = n + T
+    B = 640
+    ws = max(0, (L + B - 1) // B - 1 - (win + B - 1) // B) * B
+    low = NKV * ((32 * kbits + 16) + (32 * vbits + 16))
+    q8 = NKV * 2 * 272
+    return ws * low + (L - ws) * q8 + T * NH * HD * 2 + T * NH * HD * 4
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs"""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                c = [x.strip() for x in line.split(",")]
+                if len(c) < 9:
+                    continue
+                try:
+                    sm.append(float(c[1])); mx.append(float(c[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def run_reference(args):
+    """The CPU arm: the oracle's append + attention of one layer at the same context, all host threads; rank 0 only."""
+    rank, _, _ = dist_env()
+    if rank != 0:
+        return
+    import numpy as np
+    import kv_oracle as ko
+    import kvdata
+    cores = os.cpu_count() or 1
+    L = CTX0
+    orc = ko.Cache(1, L + 64 * T_STEP + 64, SPEC, WIN)
+    for a in range(0, L, 8192):
+        K, V = kvdata.kv_rows(2, 0, a, min(8192, L - a))
+        orc.append(0, a, K, V)
+    n = L
+    rng = np.random.default_rng(2)
+    times = []
+    total = args.warmup + args.steps
+    for s in range(total):
+        T = ko.att_cap_T(n, T_STEP)
+        K, V = kvdata.kv_rows(3, 0, n, T)
+        Q = kvdata.q_rows(3, 0, n, T)
+        t0 = time.perf_counter()
+        orc.append(0, n, K, V)
+        orc.attend(0, n, Q, threads=cores)
+        dt = time.perf_counter() - t0
+        if s >= args.warmup:
+            times.append(dt)
+        n += int(rng.integers(1, T + 1))
+    us = 1e6 * sum(times) / len(times)
+    sample = "%d layer-steps (append + attend of one layer, T=%d, n~%d) of the same workload" % (len(times), T_STEP, CTX0)
+    line = {"impl": "reference", "metric": "decode_attn_us_per_layer", "value": us, "unit": "us/layer", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": us * LAYERS / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 operands / f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "timed": "one layer per step on the host cores (a step of the full workload is 16 such layers)"},
+            "cpu_baseline": {"value": us, "unit": "us/layer", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": us, "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gb_per_s": algorithmic_bytes(CTX0, T_STEP) / us / 1e3}
+    print(json.dumps(line))
+
+
+def cpu_baseline_sample(seconds=12.0):
+    """bounded CPU sample for the cpu_baseline object of our own line"""
+    import numpy as np
+    import kv_oracle as ko
+    import kvdata
+    cores = os.cpu_count() or 1
+    L = CTX0
+    orc = ko.Cache(1, L + 64, SPEC, WIN)
+    for a in range(0, L, 8192):
+        K, V = kvdata.kv_rows(2, 0, a, min(8192, L - a))
+        orc.append(0, a, K, V)
+    Q = kvdata.q_rows(3, 0, L - T_STEP, T_STEP)
+    orc.attend(0, L - T_STEP, Q, threads=cores)
+    times = []
+    t_end = time.perf_counter() + seconds
+    while time.perf_counter() < t_end or len(times) < 3:
+        K, V = kvdata.kv_rows(3, 0, L - T_STEP, T_STEP)
+        t0 = time.perf_counter()
+        orc.append(0, L - T_STEP, K, V)
+        orc.attend(0, L - T_STEP, Q, threads=cores)
+        times.append(time.perf_counter() - t0)
+    us = 1e6 * sum(times) / len(times)
+    return {"value": us, "unit": "us/layer", "cores": cores, "kind": "port",
+            "sample": "%d layer-steps of append + attend (T=8, context 101,600) by the CPU restatement of the reference's kernels" % len(times)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--ctx", type=int, default=CTX0)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--eager", action="store_true", help="dual-write every row at append instead of spilling on eviction")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else max(args.warmup, 1)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import numpy as np
+    import torch
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    mk = importlib.import_module("qwen38-megakernel_b200")
+    mk.load_library()  # no fallback: fails here when the CUDA library is missing
+    layers, ctx0 = args.layers, args.ctx
+    total_steps = args.warmup + 2 * args.steps + 8
+    cap = ctx0 + total_steps * T_STEP + 64
+    stream = torch.cuda.current_stream()
+    eng = mk.Engine(layers, cap, SPEC, WIN, spill=not args.eager, stream=stream)
+
+    # synthetic cache: N(0,1) x per-channel scale U(0.5, 2), 1 % of channels x 20, seeded per rank and layer
+    g = torch.Generator(device="cuda")
+    def chscale(layer, side):
+        g.manual_seed(1000 * (rank + 1) + 2 * layer + side)
+        ch = torch.rand((NKV, HD), generator=g, device="cuda") * 1.5 + 0.5
+        out = torch.rand((NKV, HD), generator=g, device="cuda") < 0.01
+        return torch.where(out, ch * 20.0, ch)
+    scales = [[chscale(l, s) for s in range(2)] for l in range(layers)]
+    def rows(layer, n):
+        K = (torch.randn((n, NKV, HD), generator=g, device="cuda") * scales[layer][0]).half()
+        V = (torch.randn((n, NKV, HD), generator=g, device="cuda") * scales[layer][1]).half()
+        return K, V
+    g.manual_seed(7 + rank)
+    for l in range(layers):
+        for a in range(0, ctx0, 16384):
+            K, V = rows(l, min(16384, ctx0 - a))
+            eng.append(l, a, K, V)
+    eng.commit(ctx0)
+    eng.sync()
+
+    # per-step inputs, device resident (value) and pinned host (e2e)
+    rng = np.random.default_rng(2)
+    accepted = rng.integers(1, T_STEP + 1, size=total_steps)
+    Kd = [None] * layers; Vd = [None] * layers
+    for l in range(layers):
+        Kd[l], Vd[l] = rows(l, T_STEP)
+    Qd = torch.randn((layers, T_STEP, NH, HD), generator=g, device="cuda").half()
+    Od = torch.empty((layers, T_STEP, NH, HD), dtype=torch.float32, device="cuda")
+    Kh = torch.stack(Kd).cpu().pin_memory(); Vh = torch.stack(Vd).cpu().pin_memory(); Qh = Qd.cpu().pin_memory()
+    Oh = torch.empty((layers, T_STEP, NH, HD), dtype=torch.float32).pin_memory()
+    Ks = torch.empty_like(torch.stack(Kd)); Vs = torch.empty_like(Ks); Qs = torch.empty_like(Qd)
+
+    state = {"n": ctx0, "i": 0, "bytes": 0}
+    def one_step(host=False, time_attend=None):
+        n = state["n"]
+        T = mk.cap_T(n, T_STEP)
+        for l in range(layers):
+            if host:  # end to end: this step's rows come from pinned host memory, the result goes back
+                Ks[l].copy_(Kh[l], non_blocking=True); Vs[l].copy_(Vh[l], non_blocking=True); Qs[l].copy_(Qh[l], non_blocking=True)
+                k, v, q = Ks[l], Vs[l], Qs[l]
+            else:
+                k, v, q = Kd[l], Vd[l], Qd[l]
+            eng.append_raw(l, n, T, k, v)
+            if time_attend is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            eng.attend(l, n, q[:T], Od[l, :T])
+            if time_attend is not None:
+                e1.record(stream)
+                time_attend.append((e0, e1))
+            if host:
+                Oh[l].copy_(Od[l], non_blocking=True)
+            state["bytes"] += algorithmic_bytes(n, T)
+        if host:
+            stream.synchronize()  # the caller reads the step's result
+        state["n"] = n + min(T, int(accepted[state["i"]]))
+        state["i"] += 1
+        eng.commit(state["n"])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    # --- device-resident timing: whole steps ---
+    barrier()
+    sampler.start()
+    l0 = eng.launches()
+    state["bytes"] = 0
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        one_step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = eng.launches() - l0
+    step_bytes = state["bytes"]
+    # --- the attention launch alone (dominant kernel + its merge), event pair per launch, same stream ---
+    pairs = []
+    state["bytes"] = 0
+    for _ in range(min(args.steps, 8)):
+        one_step(time_attend=pairs)
+    torch.cuda.synchronize()
+    att_ms = [a.elapsed_time(b) for a, b in pairs]
+    att_bytes = state["bytes"] / len(pairs)
+    att_us = 1e3 * sum(att_ms) / len(att_ms)
+    # --- end to end: host buffers in, host result out, every step ---
+    one_step(host=True)
+    barrier()
+    h0 = torch.cuda.Event(enable_timing=True); h1 = torch.cuda.Event(enable_timing=True)
+    h0.record(stream)
+    for _ in range(args.steps):
+        one_step(host=True)
+    h1.record(stream)
+    barrier()
+    ms_e2e = h0.elapsed_time(h1)
+    clocks = sampler.stop()
+    eng.sync()
+
+    if dist is not None:
+        t = torch.tensor([ms, ms_e2e, att_us], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e, att_us = [float(x) for x in t.tolist()]
+    if rank == 0:
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            peak, peak_src = float(peaks["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            peak, peak_src = 6650.0, "fallback"
+        units = layers * args.steps * world
+        us_layer = 1e3 * ms / (layers * args.steps)
+        achieved = att_bytes / att_us / 1e3  # GB/s
+        line = {
+            "metric": "decode_attn_us_per_layer", "value": 1e3 * ms / units, "unit": "us/layer", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 operands / f32 accumulate over u8 packed 5/6/8-bit rows", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": layers, "context": ctx0, "queries": T_STEP, "kv_spec": SPEC, "kv_win": WIN,
+                       "mode": "eager dual-write" if args.eager else "spill on eviction (fp16 shadow)", "sequences": world,
+                       "parallelism": "independent sequence per GPU, no collective",
+                       "l2": "inputs larger than L2: %.0f MB per layer, %.2f GB per step" % (att_bytes / 1e6, att_bytes * layers / 1e9)},
+            "per_gpu_us_per_layer": us_layer,
+            "hbm_gbs_step": step_bytes / (ms * 1e-3) / 1e9 * world,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "kernel": "attn_split_kernel (+ merge)", "us_per_launch": att_us, "bytes_per_launch": att_bytes, "peak_source": peak_src},
+            "e2e": {"value": 1e3 * ms_e2e / units, "unit": "us/layer",
+                    "h2d_bytes_per_step": int(layers * (2 * T_STEP * NKV * HD * 2 + T_STEP * NH * HD * 2)),
+                    "d2h_bytes_per_step": int(layers * T_STEP * NH * HD * 4)},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline_sample()
+        print(json.dumps(line))
+    eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -132,6 +132,8 @@ int mk_kv_bits(void * h, int side, int layer);
 int mk_kv_has_ring(void * h, int side, int layer);
 int mk_kv_ring_rows(void * h);
 long long mk_kv_device_bytes(void * h);
+/* kernels this engine has launched so far (append, spill, refill, attention split and merge) */
+long long mk_kv_launches(void * h);
 
 #ifdef __cplusplus
 }

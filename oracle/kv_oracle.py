@@ -133,12 +133,15 @@ class Cache:
         self.rc = lib().orc_ring_rows(self.h)
 
     def close(self):
-        if self.h:
+        if getattr(self, "h", None):
             lib().orc_free(self.h)
             self.h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown
+            pass
 
     def bits(self, w, layer):
         return lib().orc_bits(self.h, w, layer)

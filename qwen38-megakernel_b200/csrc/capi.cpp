@@ -341,6 +341,14 @@ int mk_kv_has_ring(void * hp, int side, int layer) {
 int mk_kv_ring_rows(void * hp) {
     return guarded(hp, [](KvEngine * e) { return e->ring_rows(); });
 }
+long long mk_kv_launches(void * hp) {
+    long long r = -1;
+    guarded(hp, [&](KvEngine * e) {
+        r = e->launches();
+        return 0;
+    });
+    return r;
+}
 long long mk_kv_device_bytes(void * hp) {
     long long r = -1;
     guarded(hp, [&](KvEngine * e) {

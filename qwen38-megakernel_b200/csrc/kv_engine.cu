@@ -331,6 +331,7 @@ void KvEngine::wait_copies(Seq & s) {
 void KvEngine::spill_to(Seq & s, int layer, int upto) {
     if (!cfg_.spill || upto <= s.spilled[layer]) return;
     MKKV_CK(launch_spill(s.d_views + layer, 1, s.spilled[layer], upto, stream_));
+    launches_++;
     s.spilled[layer] = upto;
 }
 
@@ -351,10 +352,12 @@ void KvEngine::append(int seq, int layer, int pos0, int n, const void * K, const
             const int p = pos0 + done, m = std::min(n - done, rc_);
             spill_to(s, layer, std::min(p, p + m - rc_));
             MKKV_CK(launch_append(s.views[layer], k + (size_t) done * NKV * HD, v + (size_t) done * NKV * HD, p, m, stream_));
+            launches_++;
             done += m;
         }
     } else {
         MKKV_CK(launch_append(s.views[layer], k, v, pos0, n, stream_));
+        launches_++;
     }
     s.kv_top = std::max(s.kv_top, pos0 + n);
 }
@@ -412,6 +415,7 @@ void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O
     j.item0 = 0;
     spill_to(s, layer, j.ws); // positions that left the window are read in the main format from now on
     MKKV_CK(launch_attend(nullptr, &j, 1, NKV * j.nch, T, part_, ml_, d_status_, stream_));
+    launches_ += 2;
 }
 
 void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n, const int * T, const void * K, const void * V, const void * Q,
@@ -457,10 +461,12 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
     if (do_append) {
         MKKV_CK(cudaMemcpyAsync(d_ajobs_, h_ajobs_, sizeof(AppendJob) * njobs, cudaMemcpyHostToDevice, stream_));
         MKKV_CK(launch_append_batch(static_cast<const AppendJob *>(d_ajobs_), njobs, maxT, stream_));
+        launches_++;
     }
     MKKV_CK(cudaMemcpyAsync(d_jobs_, h_jobs_, sizeof(AttnJob) * njobs, cudaMemcpyHostToDevice, stream_));
     MKKV_CK(cudaEventRecord(ev_compute_, stream_));
     MKKV_CK(launch_attend(d_jobs_, h_jobs_, njobs, items, maxT, part_, ml_, d_status_, stream_));
+    launches_ += 2;
 }
 
 // ---- rewind ----

@@ -121,6 +121,7 @@ class KvEngine {
     int bits(int side, int layer) const { return kvb_[side][layer]; }
     bool has_ring(int side, int layer) const { return ring_[side][layer]; }
     size_t device_bytes() const { return dev_bytes_; }
+    long long launches() const { return launches_; } // kernels launched so far (every launcher call counts its kernels)
 
   private:
     struct Seq {
@@ -182,6 +183,7 @@ class KvEngine {
     Seq main_;
     std::vector<Seq> slots_;
     size_t dev_bytes_ = 0;
+    long long launches_ = 0;
 
     // attention workspace
     float * part_ = nullptr;

@@ -87,6 +87,7 @@ def load_library():
         "mk_kv_has_ring": (i, [vp, i, i]),
         "mk_kv_ring_rows": (i, [vp]),
         "mk_kv_device_bytes": (ll, [vp]),
+        "mk_kv_launches": (ll, [vp]),
     }
     for name, (res, args) in sig.items():
         f = getattr(L, name)
@@ -312,3 +313,6 @@ class Engine:
 
     def device_bytes(self):
         return self.L.mk_kv_device_bytes(self.h)
+
+    def launches(self):
+        return self.L.mk_kv_launches(self.h)

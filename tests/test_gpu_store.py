@@ -108,8 +108,9 @@ def test_truncate_refills(mk, torch_cuda):
     eng.close()
 
 
-def test_side_request_round_trip(mk, torch_cuda):
+def test_side_request_round_trip(mk, torch_cuda, monkeypatch):
     torch = torch_cuda
+    monkeypatch.setenv("MK_STORE_CHUNK_MIB", "4")
     spec, win, L = "K*=5r,V*=6", 2048, 5000
     eng = mk.Engine(2, L + 64, spec, win)
     orc = ko.Cache(2, L + 64, spec, win)
@@ -126,7 +127,7 @@ def test_side_request_round_trip(mk, torch_cuda):
     assert eng.side_end() and not eng.side_active()
     assert eng.position() == L and np.array_equal(eng.state_digest(), d0)
     # store too small: the kept sequence is dropped, the engine is reset
-    eng.store_budget(32 << 20)
+    eng.store_budget(16 << 20)  # the kept rows need ~27 MB
     assert eng.side_begin()
     for layer in range(2):
         fill_both(torch, eng, None, layer, 0, 4000, seed=78)
