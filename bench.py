@@ -189,7 +189,7 @@ def main():
     mk = importlib.import_module("qwen38-megakernel_b200")
     mk.load_library()  # no fallback: fails here when the CUDA library is missing
     layers, ctx0 = args.layers, args.ctx
-    total_steps = args.warmup + 2 * args.steps + 8
+    total_steps = args.warmup + 2 * args.steps + 16
     cap = ctx0 + total_steps * T_STEP + 64
     stream = torch.cuda.current_stream()
     eng = mk.Engine(layers, cap, SPEC, WIN, spill=not args.eager, stream=stream)
