@@ -59,6 +59,17 @@ int mk_kv_append(void * h, int seq, int layer, int pos0, int n, const void * K, 
  * (their rows already appended), causal among the T. Q fp16 [T][24][256] (post-norm, post-RoPE, unscaled), O fp32
  * [T][24][256]. 0 / -1 */
 int mk_kv_attend(void * h, int seq, int layer, int n, int T, const void * Q, void * O);
+/* No counterpart in the reference. mk_kv_attend for callers that must not touch the CUDA allocator while they decode: a
+ * plugin inside a server that has already handed every byte of device memory to its own pool (a cudaMalloc there fails or
+ * stalls the whole device), or a real-time loop that may not take the allocator's locks and implicit synchronisation.
+ * Same arguments, same result. The split-K partials go to a fixed array compiled into the library (3.96 MB on every GPU
+ * that loads it, until the process exits) instead of the engine's allocated workspace; the call runs no cudaMalloc /
+ * cudaFree or any other allocating routine. Limits: one sequence per call, T <= 8, at most 80 (kv head, chunk) items; a call
+ * beyond that returns -1 with a message saying so. The first call on a device looks up the array's device address: make
+ * that first call before any stream capture. All handles of a process share the one array per GPU, and it keeps the last
+ * call's contents (nothing in it needs clearing: each call writes every partial it reads): two such calls that can
+ * overlap on the GPU (different streams or handles) race and must be serialised by the caller. 0 / -1 */
+int mk_kv_attend_static(void * h, int seq, int layer, int n, int T, const void * Q, void * O);
 /* append + attend of one decode step's layer, as the reference's attention phase does in one pass */
 int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O);
 /* lanes_step (lanes.cu:452-560): one pass over several sequences; job j runs T[j] tokens at n[j] of sequence seqs[j].

@@ -143,6 +143,12 @@ int mk_kv_attend(void * hp, int seq, int layer, int n, int T, const void * Q, vo
         return 0;
     });
 }
+int mk_kv_attend_static(void * hp, int seq, int layer, int n, int T, const void * Q, void * O) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->attend_static(seq, layer, n, T, Q, O);
+        return 0;
+    });
+}
 int mk_kv_step(void * hp, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O) {
     return guarded(hp, [&](KvEngine * e) {
         e->append(seq, layer, n, T, K, V);

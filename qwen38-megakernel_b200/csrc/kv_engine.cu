@@ -418,6 +418,30 @@ void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O
     launches_ += 2;
 }
 
+void KvEngine::attend_static(int seq, int layer, int n, int T, const void * Q, void * O) {
+    use_device();
+    check_layer(layer);
+    Seq & s = seq_ref(seq);
+    if (T < 1 || T > MAXT) throw std::runtime_error("attend_static: T must be 1.." + std::to_string(MAXT) + " (the fixed scratch holds " + std::to_string(AR) + " query rows per item)");
+    if (n < 0 || n + T > s.kv_top) throw std::runtime_error("attend_static: rows up to " + std::to_string(n + T) + " have not been appended (" + std::to_string(s.kv_top) + " written)");
+    if (!Q || !O) throw std::runtime_error("attend_static: null Q / O");
+    wait_copies(s);
+    AttnJob j;
+    j.kv = s.views[layer];
+    j.Q = static_cast<const uint16_t *>(Q);
+    j.O = static_cast<float *>(O);
+    j.n = n;
+    j.T = T;
+    attn_dims(n + T, j.nch, j.cs);
+    j.ws = kv_ws(n + T, cfg_.win);
+    j.item0 = 0;
+    if (NKV * j.nch > STATIC_ITEMS)
+        throw std::runtime_error("attend_static: the call needs " + std::to_string(NKV * j.nch) + " partial items, the fixed scratch holds " + std::to_string(STATIC_ITEMS));
+    spill_to(s, layer, j.ws);
+    MKKV_CK(launch_attend_static(j, d_status_, stream_));
+    launches_ += 2;
+}
+
 void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n, const int * T, const void * K, const void * V, const void * Q,
                           void * O, bool do_append) {
     use_device();

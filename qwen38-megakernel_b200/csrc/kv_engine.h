@@ -76,6 +76,8 @@ class KvEngine {
     // ---- the hot path ----
     void append(int seq, int layer, int pos0, int n, const void * K, const void * V);
     void attend(int seq, int layer, int n, int T, const void * Q, void * O);
+    // attend() with the split partials in the library's fixed device array: this call allocates nothing
+    void attend_static(int seq, int layer, int n, int T, const void * Q, void * O);
     // one launch sequence for several sequences: job j appends T[j] rows at n[j] and attends; packed device buffers in job order
     void step_batch(int njobs, const int * seqs, int layer, const int * n, const int * T, const void * K, const void * V, const void * Q,
                     void * O, bool do_append);

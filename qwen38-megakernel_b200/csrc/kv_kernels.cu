@@ -534,4 +534,34 @@ cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, i
     return cudaGetLastError();
 }
 
+// --------------------------------------------------------------------------------------------------------------------
+// attention with its scratch inside the device image (no allocator involved)
+// --------------------------------------------------------------------------------------------------------------------
+// In host code these names are only handles for cudaGetSymbolAddress: the kernels get the looked-up device addresses.
+static __device__ __align__(256) float g_static_part[(size_t) STATIC_ITEMS * AR * HD];
+static __device__ __align__(256) float2 g_static_ml[(size_t) STATIC_ITEMS * AR];
+
+cudaError_t launch_attend_static(const AttnJob & job, int * status, cudaStream_t stream) {
+    static float * part_addr[64] = {};
+    static float2 * ml_addr[64] = {};
+    if (NKV * job.nch > STATIC_ITEMS) return cudaErrorInvalidValue;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!part_addr[dev]) { // once per device, with that device current
+        void * p = nullptr, * m = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_part);
+        if (e != cudaSuccess) return e;
+        e = cudaGetSymbolAddress(&m, g_static_ml);
+        if (e != cudaSuccess) return e;
+        ml_addr[dev] = static_cast<float2 *>(m);
+        part_addr[dev] = static_cast<float *>(p);
+    }
+    AttnJob j = job;
+    j.item0 = 0;
+    // every partial row the merge reads is written by the split kernel of the same call: nothing has to start at zero
+    return launch_attend(nullptr, &j, 1, NKV * j.nch, j.T, part_addr[dev], ml_addr[dev], status, stream);
+}
+
 } // namespace mkkv

@@ -48,4 +48,12 @@ cudaError_t launch_gather(const CopyRegion * regions, int nregions, int a, int b
 
 size_t attend_smem_bytes();
 
+// Decode attention of ONE job whose split partials live in a fixed array inside the library's device image instead of
+// memory obtained from the CUDA allocator. The array holds STATIC_ITEMS (kv head, chunk) items: enough for any single
+// job (the partition never makes more than NKV * ATT_NCH), about 3.96 MB per GPU that loads the library, held until the
+// process exits. The first call on a device looks the array's device address up (cudaGetSymbolAddress); make that call
+// outside stream capture. Returns cudaErrorInvalidValue if the job needs more items than the array holds.
+constexpr int STATIC_ITEMS = NKV * ATT_NCH;
+cudaError_t launch_attend_static(const AttnJob & job, int * status, cudaStream_t stream);
+
 } // namespace mkkv

@@ -46,6 +46,7 @@ def load_library():
         "mk_kv_sync": (i, [vp]),
         "mk_kv_append": (i, [vp, i, i, i, i, vp, vp]),
         "mk_kv_attend": (i, [vp, i, i, i, i, vp, vp]),
+        "mk_kv_attend_static": (i, [vp, i, i, i, i, vp, vp]),
         "mk_kv_step": (i, [vp, i, i, i, i, vp, vp, vp, vp]),
         "mk_kv_reserve_batch": (i, [vp, i]),
         "mk_kv_step_batch": (i, [vp, i, ip, i, ip, ip, vp, vp, vp, vp]),
@@ -178,6 +179,10 @@ class Engine:
 
     def attend(self, layer, n, Q, O, seq=SEQ_MAIN):
         self._ck(self.L.mk_kv_attend(self.h, seq, layer, n, Q.shape[0], _ptr(Q), _ptr(O)), "attend")
+
+    def attend_static(self, layer, n, Q, O, seq=SEQ_MAIN):
+        """attend() that allocates nothing: partials go to the library's fixed device array (see mk_kv_attend_static)"""
+        self._ck(self.L.mk_kv_attend_static(self.h, seq, layer, n, Q.shape[0], _ptr(Q), _ptr(O)), "attend_static")
 
     def step(self, layer, n, K, V, Q, O, seq=SEQ_MAIN):
         self._ck(self.L.mk_kv_step(self.h, seq, layer, n, Q.shape[0], _ptr(K), _ptr(V), _ptr(Q), _ptr(O)), "step")
