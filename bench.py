@@ -322,7 +322,7 @@ def main():
             "per_gpu_us_per_layer": us_layer,
             "hbm_gbs_step": step_bytes / (ms * 1e-3) / 1e9 * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                         "kernel": "attn_split_kernel (+ merge)", "us_per_launch": att_us, "bytes_per_launch": att_bytes, "peak_source": peak_src},
+                         "kernel": "attn_fast_kernel (+ merge)", "us_per_launch": att_us, "bytes_per_launch": att_bytes, "peak_source": peak_src},
             "e2e": {"value": 1e3 * ms_e2e / units, "unit": "us/layer",
                     "h2d_bytes_per_step": int(layers * (2 * T_STEP * NKV * HD * 2 + T_STEP * NH * HD * 2)),
                     "d2h_bytes_per_step": int(layers * T_STEP * NH * HD * 4)},

@@ -143,6 +143,10 @@ int mk_kv_bits(void * h, int side, int layer);
 int mk_kv_has_ring(void * h, int side, int layer);
 int mk_kv_ring_rows(void * h);
 long long mk_kv_device_bytes(void * h);
+/* Tracing, as the reference's -DMK_PROFILE barrier stamps (qwen38_mk.cu:143, engine.cu:377-560): with MK_KV_PROFILE=1 in the
+ * environment at mk_kv_new, the decode-attention kernel records globaltimer stamps per phase for the first 16 batches of every
+ * CTA; this copies the last launch's stamps ([CTA][16][20] words, nanoseconds) and returns the word count (0: off) */
+long long mk_kv_profile(void * h, unsigned long long * out, long long cap);
 /* kernels this engine has launched so far (append, spill, refill, attention split and merge) */
 long long mk_kv_launches(void * h);
 

@@ -347,6 +347,17 @@ int mk_kv_has_ring(void * hp, int side, int layer) {
 int mk_kv_ring_rows(void * hp) {
     return guarded(hp, [](KvEngine * e) { return e->ring_rows(); });
 }
+long long mk_kv_profile(void * hp, unsigned long long * out, long long cap) {
+    long long r = -1;
+    guarded(hp, [&](KvEngine * e) {
+        const auto v = e->profile();
+        if (out)
+            for (long long i = 0; i < std::min<long long>((long long) v.size(), cap); i++) out[i] = v[i];
+        r = (long long) v.size();
+        return 0;
+    });
+    return r;
+}
 long long mk_kv_launches(void * hp) {
     long long r = -1;
     guarded(hp, [&](KvEngine * e) {

@@ -45,6 +45,8 @@ void cuda_fail(cudaError_t e, const char * what, const char * file, int line) {
     throw MKCudaError(msg);
 }
 
+constexpr int XCH_NB = 64; // batches per chunk the exchange arrays of the fast attention kernel hold
+
 namespace {
 bool parse_spec(const std::string & str, int layers, int (*kvb)[MAX_LAYERS], int (*rot)[MAX_LAYERS]) {
     // MK_KV grammar: comma-separated <K|V|*><layer|*|empty>=<4..8>[r] (loader.cu:1329-1366)
@@ -107,8 +109,34 @@ KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
         const long v = atol(c);
         if (v >= 1 && v <= 1024) hs_chunk_ = (size_t) v << 20;
     }
+    MKKV_CK(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, dev_));
+    if (const char * c = getenv("MK_KV_ATTN")) use_fast_ = strcmp(c, "baseline") != 0; // "baseline": the simple kernel only
+    constexpr size_t XN = (size_t) NKV * ATT_NCH * XCH_NB;
+    MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&xmax_), XN * AR * sizeof(unsigned long long)));
+    MKKV_CK(cudaMemset(xmax_, 0, XN * AR * sizeof(unsigned long long)));
+    if (const char * c = getenv("MK_KV_PROFILE"))
+        if (atoi(c) > 0) {
+            MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&prof_), attend_fast_prof_words(num_sms_) * sizeof(unsigned long long)));
+            MKKV_CK(cudaMemset(prof_, 0, attend_fast_prof_words(num_sms_) * sizeof(unsigned long long)));
+        }
     alloc_seq(main_, cfg.ctx);
-    ensure_work(NKV * ATT_NCH, 1);
+    ensure_work(std::max(NKV * ATT_NCH, num_sms_), 1);
+}
+
+// the decode-attention launches of one call: the fast kernel, or the baseline one for shapes it does not take
+void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items, int max_T) {
+    if (use_fast_) {
+        const cudaError_t e = launch_attend_fast(d_jobs_, jobs_host, njobs, items, max_T, num_sms_, part_, ml_, work_items_, xmax_,
+                                                 XCH_NB, ++epoch_, d_status_, njobs == 1 ? prof_ : nullptr, true, stream_);
+        if (e == cudaSuccess) {
+            launches_ += 2;
+            return;
+        }
+        if (e != cudaErrorNotSupported && e != cudaErrorCooperativeLaunchTooLarge) MKKV_CK(e);
+        cudaGetLastError();
+    }
+    MKKV_CK(launch_attend(d_jobs_, jobs_host, njobs, items, max_T, part_, ml_, d_status_, stream_));
+    launches_ += 2;
 }
 
 KvEngine::~KvEngine() {
@@ -129,6 +157,8 @@ KvEngine::~KvEngine() {
     cudaFree(d_ajobs_);
     cudaFreeHost(h_ajobs_);
     cudaFree(staging_);
+    cudaFree(xmax_);
+    cudaFree(prof_);
     cudaFreeHost(h_status_);
     cudaEventDestroy(ev_compute_);
     cudaEventDestroy(ev_copy_);
@@ -393,7 +423,7 @@ void KvEngine::ensure_work(int items, int njobs) {
 void KvEngine::reserve_batch(int njobs) {
     use_device();
     if (njobs < 1 || njobs > 4096) throw std::runtime_error("reserve_batch: njobs out of range");
-    ensure_work(njobs * NKV * ATT_NCH, njobs);
+    ensure_work(std::max(njobs * NKV * ATT_NCH, num_sms_), njobs);
 }
 
 void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O) {
@@ -414,8 +444,7 @@ void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O
     j.ws = kv_ws(n + T, cfg_.win);
     j.item0 = 0;
     spill_to(s, layer, j.ws); // positions that left the window are read in the main format from now on
-    MKKV_CK(launch_attend(nullptr, &j, 1, NKV * j.nch, T, part_, ml_, d_status_, stream_));
-    launches_ += 2;
+    launch_attention(&j, 1, NKV * j.nch, T);
 }
 
 void KvEngine::attend_static(int seq, int layer, int n, int T, const void * Q, void * O) {
@@ -489,8 +518,7 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
     }
     MKKV_CK(cudaMemcpyAsync(d_jobs_, h_jobs_, sizeof(AttnJob) * njobs, cudaMemcpyHostToDevice, stream_));
     MKKV_CK(cudaEventRecord(ev_compute_, stream_));
-    MKKV_CK(launch_attend(d_jobs_, h_jobs_, njobs, items, maxT, part_, ml_, d_status_, stream_));
-    launches_ += 2;
+    launch_attention(h_jobs_, njobs, items, maxT);
 }
 
 // ---- rewind ----
@@ -1019,6 +1047,16 @@ std::vector<unsigned long long> KvEngine::state_digest(int seq) {
                 }
             }
     return out;
+}
+
+std::vector<unsigned long long> KvEngine::profile() {
+    use_device();
+    std::vector<unsigned long long> v;
+    if (!prof_) return v;
+    sync();
+    v.resize(attend_fast_prof_words(num_sms_));
+    MKKV_CK(cudaMemcpy(v.data(), prof_, v.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return v;
 }
 
 int KvEngine::read_row(int seq, int layer, int side, int g, int pos, bool ring, void * val, void * sc) {

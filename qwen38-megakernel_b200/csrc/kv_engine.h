@@ -123,6 +123,7 @@ class KvEngine {
     int bits(int side, int layer) const { return kvb_[side][layer]; }
     bool has_ring(int side, int layer) const { return ring_[side][layer]; }
     size_t device_bytes() const { return dev_bytes_; }
+    std::vector<unsigned long long> profile(); // MK_KV_PROFILE=1: the stamps of the last fast attention launch (else empty)
     long long launches() const { return launches_; } // kernels launched so far (every launcher call counts its kernels)
 
   private:
@@ -198,6 +199,12 @@ class KvEngine {
     int work_jobs_ = 0;
     int * h_status_ = nullptr; // mapped pinned word the kernels write
     int * d_status_ = nullptr;
+    // fast attention path: exchange of row maxima between the CTAs of one chunk
+    unsigned long long * xmax_ = nullptr;
+    int epoch_ = 0, num_sms_ = 0;
+    bool use_fast_ = true;
+    unsigned long long * prof_ = nullptr; // MK_KV_PROFILE=1: phase stamps of the last fast attention launch
+    void launch_attention(const AttnJob * jobs_host, int njobs, int items, int max_T);
 
     // host store
     size_t hs_chunk_ = (size_t) 32 << 20, hs_budget_ = 0, hs_alloc_ = 0;

@@ -246,6 +246,7 @@ struct AttnSmem {
     float m[AR], l[AR], al[AR];
     uint64_t full[A_STAGES];
     int job;
+    AttnJob jobc; // the CTA's job, copied once: no parameter / global reads inside the tile loop
 };
 size_t attend_smem_bytes() { return sizeof(AttnSmem) + 128; }
 
@@ -306,7 +307,13 @@ __global__ void __launch_bounds__(A_THREADS, 1) attn_split_kernel(const __grid_c
         mbar_fence_init();
     }
     __syncthreads();
-    const AttnJob & J = a.jobs ? a.jobs[sm.job] : a.one;
+    {
+        const unsigned * src = reinterpret_cast<const unsigned *>(a.jobs ? &a.jobs[sm.job] : &a.one);
+        unsigned * dst = reinterpret_cast<unsigned *>(&sm.jobc);
+        for (int i = tid; i < (int) (sizeof(AttnJob) / 4); i += A_THREADS) dst[i] = src[i];
+    }
+    __syncthreads();
+    const AttnJob & J = sm.jobc;
     const int T = J.T, n = J.n, R = GQ * T, MT = (R + 15) >> 4, L = n + T;
     const int item = (int) blockIdx.x - J.item0, g = item / J.nch, c = item % J.nch;
     const int c0 = c * J.cs, c1 = min(L, c0 + J.cs), ntiles = (c1 - c0 + ATP - 1) / ATP;
@@ -534,6 +541,20 @@ cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, i
     return cudaGetLastError();
 }
 
+cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,
+                         cudaStream_t stream) {
+    AttnArgs a;
+    a.one = jobs_host[0];
+    a.jobs = njobs > 1 ? jobs_dev : nullptr;
+    a.njobs = njobs;
+    a.part = part;
+    a.ml = ml;
+    a.status = nullptr;
+    const int rows_per_job = NH * max_T;
+    attn_merge_kernel<<<(njobs * rows_per_job + 7) / 8, 256, 0, stream>>>(a, rows_per_job);
+    return cudaGetLastError();
+}
+
 // --------------------------------------------------------------------------------------------------------------------
 // attention with its scratch inside the device image (no allocator involved)
 // --------------------------------------------------------------------------------------------------------------------
@@ -560,7 +581,11 @@ cudaError_t launch_attend_static(const AttnJob & job, int * status, cudaStream_t
     }
     AttnJob j = job;
     j.item0 = 0;
-    // every partial row the merge reads is written by the split kernel of the same call: nothing has to start at zero
+    // every partial row the merge reads is written by the split kernel of the same call: nothing has to start at zero.
+    // One CTA per (kv head, chunk): that mode of the fast kernel needs no other scratch than the partials.
+    const cudaError_t fe = launch_attend_fast(nullptr, &j, 1, NKV * j.nch, j.T, 0, part_addr[dev], ml_addr[dev], STATIC_ITEMS, nullptr, 0, 0,
+                                              status, nullptr, false, stream);
+    if (fe != cudaErrorNotSupported) return fe;
     return launch_attend(nullptr, &j, 1, NKV * j.nch, j.T, part_addr[dev], ml_addr[dev], status, stream);
 }
 

@@ -24,6 +24,22 @@ cudaError_t launch_refill(const KvView * views, int layers, int p0, int p1, cuda
 cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
                           float2 * ml, int * status, cudaStream_t stream);
 
+// the merge alone: job j's partials are slots item0 + g nch .. + nch - 1 of kv head g
+cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,
+                         cudaStream_t stream);
+// Fast path (kv_attend_fast.cu): same result as launch_attend. One job: cooperative launch over num_sms CTAs with an
+// exchange of row maxima through xmax ([4][20][nbmax][48] 8-byte words {epoch, value}, zeroed once; epoch must be non-zero and
+// differ from every earlier launch's). Several jobs: one CTA per (job, kv head, chunk). part / ml hold part_slots partials.
+// cudaErrorNotSupported: shape not handled (use launch_attend).
+cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, int num_sms,
+                               float * part, float2 * ml, int part_slots, unsigned long long * xmax, int nbmax, int epoch, int * status,
+                               unsigned long long * prof, bool spread, cudaStream_t stream);
+size_t attend_fast_smem_bytes();
+// prof (optional, null: off): globaltimer stamps of the first batches of every CTA, [CTA][16][20] words: 0 batch start,
+// 1 K tile arrived, 2 scores done, 3 / 4 before / after the batch barrier, 5 incoming max known, 6 running maxima done,
+// 7 barrier, 11 P written (score warp 0); 8 / 9 / 10 batch start, first P tile arrived, batch done (first P V warp)
+size_t attend_fast_prof_words(int ctas);
+
 // batched append: job j writes n rows at pos0 of its own (sequence, layer)
 struct AppendJob {
     KvView kv;

@@ -89,6 +89,7 @@ def load_library():
         "mk_kv_ring_rows": (i, [vp]),
         "mk_kv_device_bytes": (ll, [vp]),
         "mk_kv_launches": (ll, [vp]),
+        "mk_kv_profile": (ll, [vp, ullp, ll]),
     }
     for name, (res, args) in sig.items():
         f = getattr(L, name)
@@ -318,6 +319,16 @@ class Engine:
 
     def device_bytes(self):
         return self.L.mk_kv_device_bytes(self.h)
+
+    def profile(self):
+        """phase stamps of the last decode-attention launch, [CTA][16][20] ns (needs MK_KV_PROFILE=1 at construction)"""
+        import numpy as np
+        n = self.L.mk_kv_profile(self.h, None, 0)
+        if n <= 0:
+            return None
+        out = np.zeros(n, dtype=np.uint64)
+        self.L.mk_kv_profile(self.h, out.ctypes.data_as(C.POINTER(C.c_ulonglong)), n)
+        return out.reshape(-1, 16, 20)
 
     def launches(self):
         return self.L.mk_kv_launches(self.h)
