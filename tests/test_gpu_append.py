@@ -125,3 +125,26 @@ def test_refill_after_rewind(mk, torch_cuda):
         for layer in range(2):
             assert_rows_equal(eng, orc, layer, [], ring_positions=range(5000 - 3232, 5000, 7), main=False)
         eng.close()
+
+
+@pytest.mark.parametrize("bits", [4, 5, 6, 7, 8])
+@pytest.mark.parametrize("rot", [0, 1])
+def test_append_matches_reference_golden_vectors(mk, torch_cuda, bits, rot):
+    """the CUDA append kernel against the committed golden vectors (bytes made by the reference's own device functions)"""
+    import os
+    torch = torch_cuda
+    gpath = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kv_quant_golden.npz")
+    if not os.path.exists(gpath):
+        pytest.skip("golden vectors not generated")
+    g = np.load(gpath)
+    rows = g["rows"].astype(np.float16)
+    n = rows.shape[0]
+    spec = "K*=%d%s,V*=8" % (bits, "r" if rot else "")
+    eng = mk.Engine(1, n + 8, spec, 0)
+    K = np.repeat(rows[:, None, :], 4, axis=1).copy()
+    eng.append(0, 0, torch.from_numpy(K).cuda(), torch.from_numpy(K).cuda())
+    q, sc = g["q_%d_%d" % (bits, rot)], g["sc_%d_%d" % (bits, rot)]
+    for i in range(n):
+        a, sa = eng.read_row(0, 0, 3, i)
+        assert np.array_equal(a, q[i]) and np.array_equal(sa, sc[i]), (bits, rot, i)
+    eng.close()
