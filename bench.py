@@ -29,6 +29,9 @@ for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
 LAYERS, CTX0, T_STEP, WIN = 16, 101600, 8, 2048
 SPEC = "K*=5r,V*=6"
 NH, NKV, HD = 24, 4, 256
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fast_kernel launch at this workload's shapes (ncu capture of the
+# one-layer case, profiles/attn_fast_kernel_config2_one_layer.md; a launch of the 16-layer run processes the same one layer)
+NCU_TRAFFIC_BYTES = 166.2e6
 WORKLOAD = "config2: 16 attention layers, 101,600 positions, preset F layout K5r/V6 + q8_0 window 2048, 8 queries/step, streaming append+spill+attend"
 
 
@@ -321,7 +324,7 @@ def main():
                        "l2": "inputs larger than L2: %.0f MB per layer, %.2f GB per step" % (att_bytes / 1e6, att_bytes * layers / 1e9)},
             "per_gpu_us_per_layer": us_layer,
             "hbm_gbs_step": step_bytes / (ms * 1e-3) / 1e9 * world,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES if (layers == LAYERS and ctx0 == CTX0) else None,
                          "kernel": "attn_fast_kernel (+ merge)", "us_per_launch": att_us, "bytes_per_launch": att_bytes, "peak_source": peak_src},
             "e2e": {"value": 1e3 * ms_e2e / units, "unit": "us/layer",
                     "h2d_bytes_per_step": int(layers * (2 * T_STEP * NKV * HD * 2 + T_STEP * NH * HD * 2)),

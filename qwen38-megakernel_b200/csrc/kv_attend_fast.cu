@@ -810,7 +810,7 @@ cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_ho
         // one sequence: spread its tasks over all SMs; pick the batch size that leaves the fewest idle rounds
         a.mode = 0;
         a.cph = num_sms / NKV;
-        if (a.cph < 1) return cudaErrorNotSupported;
+        if (a.cph < 1 || a.cph > 64) return cudaErrorNotSupported; // (the merge holds a kv head's partial weights in two registers per lane)
         int best_B = 0, best_cost = 0x7fffffff;
         for (int B = fast::SW; B >= 4; B--) {
             int nb_full;

@@ -486,16 +486,22 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__
     if (rr >= NH * J.T) return;
     const int h = rr / J.T, t = rr % J.T, g = h / GQ, r = (h % GQ) * J.T + t;
     const size_t i0 = (size_t) J.item0 + (size_t) g * J.nch;
-    float M = -CUDART_INF_F;
-    for (int c = 0; c < J.nch; c++) M = fmaxf(M, a.ml[(i0 + c) * AR + r].x);
+    // lane c (and c + 32) holds partial c's (m, l): all weights first, so the sums below run over independent loads
+    float2 mla = lane < J.nch ? a.ml[(i0 + lane) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
+    float2 mlb = lane + 32 < J.nch ? a.ml[(i0 + lane + 32) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
+    float M = fmaxf(mla.x, mlb.x);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) M = fmaxf(M, __shfl_xor_sync(FULL, M, m));
+    const float wa = mla.x == -CUDART_INF_F ? 0.f : expf(mla.x - M), wb = mlb.x == -CUDART_INF_F ? 0.f : expf(mlb.x - M);
     float num[8], den = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; k++) num[k] = 0.f;
-    for (int c = 0; c < J.nch; c++) {
-        const float2 ml = a.ml[(i0 + c) * AR + r];
-        const float w = ml.x == -CUDART_INF_F ? 0.f : expf(ml.x - M);
-        const float4 * o = reinterpret_cast<const float4 *>(a.part + ((i0 + c) * AR + r) * HD + lane * 8);
-        const float4 o0 = o[0], o1 = o[1];
+    const float * pbase = a.part + (i0 * AR + r) * HD + lane * 8;
+#pragma unroll 4
+    for (int c = 0; c < J.nch; c++) { // (partials beyond 64 per kv head do not occur: nch <= 20, or #SM / 4 for the fast path)
+        const float w = __shfl_sync(FULL, c < 32 ? wa : wb, c & 31), lc = __shfl_sync(FULL, c < 32 ? mla.y : mlb.y, c & 31);
+        const float4 * o = reinterpret_cast<const float4 *>(pbase + (size_t) c * AR * HD);
+        const float4 o0 = __ldcg(o), o1 = __ldcg(o + 1);
         num[0] = __fmaf_rn(w, o0.x, num[0]);
         num[1] = __fmaf_rn(w, o0.y, num[1]);
         num[2] = __fmaf_rn(w, o0.z, num[2]);
@@ -504,7 +510,7 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__
         num[5] = __fmaf_rn(w, o1.y, num[5]);
         num[6] = __fmaf_rn(w, o1.z, num[6]);
         num[7] = __fmaf_rn(w, o1.w, num[7]);
-        den = __fmaf_rn(w, ml.y, den);
+        den = __fmaf_rn(w, lc, den);
     }
     float y[8];
 #pragma unroll
