@@ -166,6 +166,96 @@ def cpu_baseline_sample(seconds=12.0):
             "sample": "%d layer-steps of append + attend (T=8, context 101,600) by the CPU restatement of the reference's kernels" % len(times)}
 
 
+def run_split(args):
+    """Config 2b: ONE sequence of --split-ctx positions split by position over the ranks; every step each rank attends its own
+    rows, the (max, sum, un-normalised output) partials are all-gathered over NCCL and merged on every rank."""
+    import numpy as np
+    import torch
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    mk = importlib.import_module("qwen38-megakernel_b200")
+    mk.load_library()
+    layers, ctx0 = args.layers, args.split_ctx
+    total_steps = args.warmup + args.steps + 4
+    cap = ctx0 + total_steps * T_STEP + 64
+    stream = torch.cuda.current_stream()
+    seq = mk.parallel.SplitSequence(mk.Engine, layers, cap, SPEC, WIN, rank, world, dist=dist, spill=not args.eager, stream=stream)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(100 + rank)
+    lo, hi = seq.lo, min(seq.hi, ctx0)
+    for l in range(layers):  # every rank fills the positions it owns (timing run: the rows need not match across ranks)
+        for a in range(lo, hi, 16384):
+            m = min(16384, hi - a)
+            K = (torch.randn((m, NKV, HD), generator=g, device="cuda") * 1.3).half()
+            V = (torch.randn((m, NKV, HD), generator=g, device="cuda") * 1.3).half()
+            seq.eng.append(l, a, K, V)
+    g.manual_seed(5)  # the step's rows and queries are replicated: same seed on every rank
+    Kd = (torch.randn((layers, T_STEP, NKV, HD), generator=g, device="cuda") * 1.3).half()
+    Vd = (torch.randn((layers, T_STEP, NKV, HD), generator=g, device="cuda") * 1.3).half()
+    Qd = torch.randn((layers, T_STEP, NH, HD), generator=g, device="cuda").half()
+    Od = torch.empty((layers, T_STEP, NH, HD), dtype=torch.float32, device="cuda")
+    rng = np.random.default_rng(2)
+    state = {"n": ctx0}
+
+    def one_step():
+        n = state["n"]
+        T = mk.cap_T(n, T_STEP)
+        for l in range(layers):
+            seq.append(l, n, Kd[l, :T], Vd[l, :T])
+            seq.attend(l, n, Qd[l, :T], Od[l, :T])
+        state["n"] = n + min(T, int(rng.integers(1, T_STEP + 1)))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    l0 = seq.eng.launches()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        one_step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = seq.eng.launches() - l0
+    clocks = sampler.stop()
+    check = float(Od.abs().max())
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        try:
+            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        except Exception:
+            peak = 6650.0
+        us_layer = 1e3 * ms / (layers * args.steps)
+        nbytes = algorithmic_bytes(ctx0, T_STEP)
+        line = {"metric": "decode_attn_us_per_layer", "value": us_layer, "unit": "us/layer", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16 operands / f32 accumulate over u8 packed 5/6/8-bit rows", "data": "synthetic",
+                "config": {"workload": "config2b: one sequence of %d positions split by position over %d GPUs, 16 layers, 8 queries/step, "
+                                       "NCCL all-gather of (max, sum, output) partials + merge" % (ctx0, world),
+                           "layers": layers, "context": ctx0, "kv_spec": SPEC, "kv_win": WIN, "combine_bytes_per_rank_layer": 4 * 48 * 258 * 4},
+                "hbm_gbs_whole_job": nbytes / (us_layer * 1e-6) / 1e9, "frac_of_measured_peak_per_gpu": nbytes / (us_layer * 1e-6) / 1e9 / peak / world,
+                "gpu_launches": int(launches), "clocks": clocks, "output_absmax": check}
+        print(json.dumps(line))
+    seq.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -176,10 +266,13 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--eager", action="store_true", help="dual-write every row at append instead of spilling on eviction")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--split-ctx", type=int, default=0, help="config 2b: one sequence of this many positions split over the GPUs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else max(args.warmup, 1)
     if args.impl == "reference":
         return run_reference(args)
+    if args.split_ctx > 0:
+        return run_split(args)
 
     import numpy as np
     import torch

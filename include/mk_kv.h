@@ -70,6 +70,16 @@ int mk_kv_attend(void * h, int seq, int layer, int n, int T, const void * Q, voi
  * call's contents (nothing in it needs clearing: each call writes every partial it reads): two such calls that can
  * overlap on the GPU (different streams or handles) race and must be serialised by the caller. 0 / -1 */
 int mk_kv_attend_static(void * h, int seq, int layer, int n, int T, const void * Q, void * O);
+/* ---- one very long sequence split by position over several GPUs (no counterpart in the reference, which is single-GPU: its
+ * split-K partials (qwen38_mk.cu:3048-3064) and merge (:4658-4669) are the unit that is exchanged) ----
+ * mk_kv_set_base: this handle's copy of sequence seq holds positions [base, base + ctx) (empty sequence; base a multiple of 32).
+ * mk_kv_attend_partial: the T tokens at n over positions [pos_lo, pos_hi) only, inside this handle's rows, with the reference's
+ * chunk partition of the WHOLE context n + T; writes the un-normalised result per kv head: part_out fp32 [4][48][256] (row
+ * (head % 6) T + t), ml_out fp32 [4][48][2] = (max, sum). Every rank passes the same Q.
+ * mk_kv_combine: merges nparts such results laid one after another (as an all-gather leaves them) into O fp32 [T][24][256]. */
+int mk_kv_set_base(void * h, int seq, int base);
+int mk_kv_attend_partial(void * h, int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out);
+int mk_kv_combine(void * h, int layer, int T, int nparts, const void * parts, const void * mls, void * O);
 /* append + attend of one decode step's layer, as the reference's attention phase does in one pass */
 int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O);
 /* lanes_step (lanes.cu:452-560): one pass over several sequences; job j runs T[j] tokens at n[j] of sequence seqs[j].

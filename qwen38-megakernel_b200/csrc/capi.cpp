@@ -143,6 +143,24 @@ int mk_kv_attend(void * hp, int seq, int layer, int n, int T, const void * Q, vo
         return 0;
     });
 }
+int mk_kv_set_base(void * hp, int seq, int base) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->set_base(seq, base);
+        return 0;
+    });
+}
+int mk_kv_attend_partial(void * hp, int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->attend_partial(seq, layer, n, T, Q, pos_lo, pos_hi, part_out, ml_out);
+        return 0;
+    });
+}
+int mk_kv_combine(void * hp, int layer, int T, int nparts, const void * parts, const void * mls, void * O) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->combine(layer, T, nparts, parts, mls, O);
+        return 0;
+    });
+}
 int mk_kv_attend_static(void * hp, int seq, int layer, int n, int T, const void * Q, void * O) {
     return guarded(hp, [&](KvEngine * e) {
         e->attend_static(seq, layer, n, T, Q, O);

@@ -19,6 +19,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <vector>
 
 #include "kv_kernels.h"
 #include "kv_quant.cuh"
@@ -78,6 +79,8 @@ struct Args {
     int nbmax;     // batches per chunk the exchange array holds
     int epoch;     // tag of this launch's words (differs from every earlier launch's)
     int * status;
+    const AttnTask * tasks; // mode 0, optional: the task list of a kv head built on the host (position-range jobs), else null
+    int ntasks;             // tasks per kv head in that list
     unsigned long long * prof; // optional: [CTA][PROF_BATCHES][PROF_STAMPS] globaltimer stamps (null: off)
 };
 constexpr int PROF_BATCHES = 16, PROF_STAMPS = 20;
@@ -169,12 +172,7 @@ __device__ __forceinline__ Geo make_geo(const AttnJob & J, int B) {
     g.ntasks_head = g.nb_last * g.nch + (g.nb_full - g.nb_last) * (g.nch - 1);
     return g;
 }
-struct Task {
-    int c, b, nb; // chunk, batch, batches of the chunk
-    int pos0;     // position of the batch's first tile
-    int c1;       // end of the chunk
-    int nt;       // tiles of the batch
-};
+typedef AttnTask Task;
 // mode 0: task t (batch-major over the chunks of one kv head); mode 1: batch t of chunk c_fixed
 __device__ __forceinline__ Task make_task(const Geo & g, int B, int mode, int t, int c_fixed) {
     Task k;
@@ -209,7 +207,7 @@ __device__ __forceinline__ int tile_src(const KvView & kv, int w, int g, int tb,
         sc = s.rsc + rr * 8;
         return 8;
     }
-    const size_t row = (size_t) g * kv.ctxp + tb;
+    const size_t row = (size_t) g * kv.ctxp + (tb - kv.base);
     val = s.val + row * row_bytes(s.bits);
     sc = s.sc + row * 8;
     return s.bits;
@@ -379,8 +377,9 @@ __device__ __forceinline__ SideSrc make_src(const KvView & kv, int w, int g, int
     SideSrc r;
     r.bits = s.bits;
     r.rb = row_bytes(s.bits);
-    r.mval = s.val + (size_t) g * kv.ctxp * r.rb;
-    r.msc = s.sc + (size_t) g * kv.ctxp * 8;
+    // (row 0 of the buffer is position kv.base: fold it in; only positions >= base are ever fetched)
+    r.mval = s.val + ((ptrdiff_t) g * kv.ctxp - kv.base) * r.rb;
+    r.msc = s.sc + ((ptrdiff_t) g * kv.ctxp - kv.base) * 8;
     r.rval = s.rval ? s.rval + (size_t) g * kv.rc * HD : nullptr;
     r.rsc = s.rval ? s.rsc + (size_t) g * kv.rc * 8 : nullptr;
     r.ring0 = s.rval ? ws : 0x7fffffff;
@@ -457,7 +456,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
     const Geo geo = make_geo(J, B);
     // the CTA's task list: mode 0: tasks kk, kk + cph, .. of kv head g; mode 1: batches 0 .. nb - 1 of its chunk
     const int t_first = a.mode == 0 ? kk : 0, t_step = a.mode == 0 ? a.cph : 1;
-    const int t_end = a.mode == 0 ? geo.ntasks_head : ((c_fixed == geo.nch - 1 ? geo.nt_last : geo.nt_full) + B - 1) / B;
+    const int t_end = a.mode == 0 ? (a.tasks ? a.ntasks : geo.ntasks_head) : ((c_fixed == geo.nch - 1 ? geo.nt_last : geo.nt_full) + B - 1) / B;
+    const AttnTask * const ttab = a.mode == 0 && a.tasks ? a.tasks : nullptr;
+    auto get_task = [&](int t) -> Task { return ttab ? ttab[t] : make_task(geo, B, a.mode, t, c_fixed); };
 
     // query rows of the kv head: fp16 -> fp32 -> (K's rotation) -> x 1/16 -> fp16 (qwen38_mk.cu:2876-2883); row = (head % 6) T + t
     for (int r = warp; r < 16 * MT; r += NTHREADS / 32) {
@@ -502,7 +503,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
         auto v_issue = [&]() {
             if (vp_t >= t_end) return;
             if (vp_j == 0) { // a new task: its geometry once, then tiles by increment
-                const Task k = make_task(geo, B, a.mode, vp_t, c_fixed);
+                const Task k = get_task(vp_t);
                 vp_nt = k.nt;
                 vp_tb = k.pos0;
                 vp_c1 = k.c1;
@@ -528,7 +529,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
                 for (int k = 0; k < 4; k++) acc[i][j][k] = 0.f;
         unsigned vcnt = 0, bcnt = 0;
         for (int t = t_first; t < t_end; t += t_step, bcnt++) {
-            const Task k = make_task(geo, B, a.mode, t, c_fixed);
+            const Task k = get_task(t);
             if (dg == 0) MKKV_STAMP(8);
             for (int j = 0; j < SW; j++) {
                 const int ps = (bcnt & 1) * SW + j;
@@ -590,11 +591,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
         float m_acc = -CUDART_INF_F, l_acc = 0.f, carry = -CUDART_INF_F;
         unsigned kuse = 0, bcnt = 0;
         if (lane == 0 && t_first < t_end) { // the warp's first tile
-            const Task k = make_task(geo, B, a.mode, t_first, c_fixed);
+            const Task k = get_task(t_first);
             if (warp < k.nt) issue_tile(ksrc, k.pos0 + warp * ATP, k.c1, sm.kst[warp], &sm.k_full[warp]);
         }
         for (int t = t_first; t < t_end; t += t_step, bcnt++) {
-            const Task k = make_task(geo, B, a.mode, t, c_fixed);
+            const Task k = get_task(t);
             const int ps = (bcnt & 1) * SW + warp;
             float acc[3][4][4];
             const bool mine = warp < k.nt;
@@ -617,7 +618,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
             __syncwarp();
             if (warp == 0) MKKV_STAMP(2);
             if (lane == 0 && t + t_step < t_end) { // the stage is free: fetch this warp's tile of the next task
-                const Task kn = make_task(geo, B, a.mode, t + t_step, c_fixed);
+                const Task kn = get_task(t + t_step);
                 if (warp < kn.nt) issue_tile(ksrc, kn.pos0 + warp * ATP, kn.c1, sm.kst[warp], &sm.k_full[warp]);
             }
             if (mine) {
@@ -771,6 +772,27 @@ static int fast_tasks_per_head(const AttnJob & J, int B, int & nb_full) {
     return nb_last * J.nch + (nb_full - nb_last) * (J.nch - 1);
 }
 
+// Host-built task list for a job restricted to positions [pos_lo, pos_hi): the chunks of the partition clipped to the range,
+// cut into batches of B tiles, batch-major so that a batch's predecessors (same chunk) are always earlier in the list.
+int build_range_tasks(const AttnJob & J, int B, std::vector<AttnTask> & out) {
+    out.clear();
+    const int L = J.n + J.T;
+    struct Ch { int c, c0, c1, ntc, nb; };
+    std::vector<Ch> chs;
+    int max_nb = 0;
+    for (int c = 0; c < J.nch; c++) {
+        const int c0 = std::max(c * J.cs, J.pos_lo), c1 = std::min(std::min(L, (c + 1) * J.cs), J.pos_hi);
+        if (c1 <= c0) continue;
+        const int ntc = (c1 - c0 + ATP - 1) / ATP, nb = (ntc + B - 1) / B;
+        chs.push_back({c, c0, c1, ntc, nb});
+        max_nb = std::max(max_nb, nb);
+    }
+    for (int b = 0; b < max_nb; b++)
+        for (const Ch & h : chs)
+            if (b < h.nb) out.push_back({h.c, b, h.nb, h.c0 + b * B * ATP, h.c1, std::min(B, h.ntc - b * B)});
+    return max_nb;
+}
+
 template <int MT> static cudaError_t fast_launch_mt(const fast::Args & a, int grid, bool cooperative, cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
@@ -792,9 +814,12 @@ template <int MT> static cudaError_t fast_launch_mt(const fast::Args & a, int gr
 
 cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, int num_sms,
                                float * part, float2 * ml, int part_slots, unsigned long long * xmax, int nbmax, int epoch, int * status,
-                               unsigned long long * prof, bool spread, cudaStream_t stream) {
+                               unsigned long long * prof, bool spread, cudaStream_t stream, const AttnTask * tasks_dev, int ntasks,
+                               int tasks_B, float * raw_part, float2 * raw_ml) {
     fast::Args a;
     a.prof = prof;
+    a.tasks = nullptr;
+    a.ntasks = 0;
     a.one = jobs_host[0];
     a.jobs = njobs > 1 ? jobs_dev : nullptr;
     a.njobs = njobs;
@@ -822,6 +847,11 @@ cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_ho
                 best_B = B;
             }
         }
+        if (tasks_dev) { // a position-range job: the host built its task list with tasks_B tiles per batch
+            best_B = tasks_B;
+            a.tasks = tasks_dev;
+            a.ntasks = ntasks;
+        }
         if (!best_B) return cudaErrorNotSupported;
         a.B = best_B;
         grid = NKV * a.cph;
@@ -840,7 +870,7 @@ cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_ho
                     : MT == 2 ? fast_launch_mt<2>(a, grid, a.mode == 0, stream)
                               : fast_launch_mt<3>(a, grid, a.mode == 0, stream);
     if (e != cudaSuccess) return e;
-    return launch_merge(jobs_dev, a.mode == 0 ? &merge_job : jobs_host, njobs, max_T, part, ml, stream);
+    return launch_merge(jobs_dev, a.mode == 0 ? &merge_job : jobs_host, njobs, max_T, part, ml, stream, raw_part, raw_ml);
 }
 
 } // namespace mkkv

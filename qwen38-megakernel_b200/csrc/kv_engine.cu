@@ -156,6 +156,8 @@ KvEngine::~KvEngine() {
     cudaFreeHost(h_jobs_);
     cudaFree(d_ajobs_);
     cudaFreeHost(h_ajobs_);
+    cudaFree(d_tasks_);
+    cudaFreeHost(h_tasks_);
     cudaFree(staging_);
     cudaFree(xmax_);
     cudaFree(prof_);
@@ -219,6 +221,7 @@ void KvEngine::alloc_seq(Seq & s, int ctx) {
             v.rc = rc_;
             v.win = cfg_.win;
             v.eager = cfg_.spill ? 0 : 1;
+            v.base = 0;
             for (int w = 0; w < 2; w++) { // layers packed one after another in each side's allocation (loader.cu:1457-1468)
                 KvSide & sd = v.s[w];
                 sd.bits = kvb_[w][l];
@@ -369,7 +372,8 @@ void KvEngine::append(int seq, int layer, int pos0, int n, const void * K, const
     use_device();
     check_layer(layer);
     Seq & s = seq_ref(seq);
-    if (n < 0 || pos0 < 0 || (long long) pos0 + n > s.ctx) throw std::runtime_error("append: rows " + std::to_string(pos0) + " + " + std::to_string(n) + " exceed the context " + std::to_string(s.ctx));
+    if (n < 0 || pos0 < s.base || (long long) pos0 + n - s.base > s.ctx)
+        throw std::runtime_error("append: rows " + std::to_string(pos0) + " + " + std::to_string(n) + " outside the sequence's rows [" + std::to_string(s.base) + ", " + std::to_string(s.base + s.ctx) + ")");
     if (n == 0) return;
     if (!K || !V) throw std::runtime_error("append: null K / V");
     if (seq == SEQ_MAIN && sw_on_) sw_need(pos0 + n);
@@ -443,8 +447,93 @@ void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O
     attn_dims(n + T, j.nch, j.cs);
     j.ws = kv_ws(n + T, cfg_.win);
     j.item0 = 0;
+    j.pos_lo = 0;
+    j.pos_hi = n + T;
+    j.pstride = 1;
     spill_to(s, layer, j.ws); // positions that left the window are read in the main format from now on
     launch_attention(&j, 1, NKV * j.nch, T);
+}
+
+void KvEngine::set_base(int seq, int base) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    if (s.n != 0 || s.kv_top != 0) throw std::runtime_error("set_base: the sequence is not empty");
+    if (base < 0 || base % ATP) throw std::runtime_error("set_base: the base must be a non-negative multiple of 32");
+    MKKV_CK(cudaStreamSynchronize(stream_));
+    s.base = base;
+    for (auto & v : s.views) v.base = base;
+    MKKV_CK(cudaMemcpy(s.d_views, s.views.data(), sizeof(KvView) * cfg_.layers, cudaMemcpyHostToDevice));
+    std::fill(s.spilled.begin(), s.spilled.end(), base);
+    s.kv_top = s.n = 0;
+}
+
+void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out) {
+    use_device();
+    check_layer(layer);
+    Seq & s = seq_ref(seq);
+    if (T < 1 || T > MAXT) throw std::runtime_error("attend_partial: T must be 1.." + std::to_string(MAXT));
+    if (!Q || !part_out || !ml_out) throw std::runtime_error("attend_partial: null argument");
+    const int L = n + T;
+    if (pos_hi != pos_lo && (pos_lo % ATP || pos_lo < s.base || pos_hi > L || pos_hi < pos_lo || (pos_hi != L && pos_hi % ATP)))
+        throw std::runtime_error("attend_partial: bad position range [" + std::to_string(pos_lo) + ", " + std::to_string(pos_hi) + ")");
+    if (pos_hi > pos_lo && pos_hi > s.kv_top) throw std::runtime_error("attend_partial: rows up to " + std::to_string(pos_hi) + " have not been appended (" + std::to_string(s.kv_top) + " written)");
+    if (!use_fast_) throw std::runtime_error("attend_partial needs the fast attention kernel (MK_KV_ATTN=baseline is set)");
+    wait_copies(s);
+    AttnJob j;
+    j.kv = s.views[layer];
+    j.Q = static_cast<const uint16_t *>(Q);
+    j.O = nullptr;
+    j.n = n;
+    j.T = T;
+    attn_dims(L, j.nch, j.cs);
+    j.ws = kv_ws(L, cfg_.win);
+    j.item0 = 0;
+    j.pos_lo = pos_lo;
+    j.pos_hi = pos_hi;
+    j.pstride = 1;
+    if (pos_hi > pos_lo) spill_to(s, layer, std::min(j.ws, pos_hi)); // rows of this range that left the window
+    std::vector<AttnTask> tasks;
+    const int B = 8, max_nb = build_range_tasks(j, B, tasks);
+    if (max_nb > XCH_NB) throw std::runtime_error("attend_partial: the context is too long for the exchange buffers");
+    const int nt = (int) tasks.size();
+    if (nt > tasks_cap_) {
+        MKKV_CK(cudaStreamSynchronize(stream_));
+        cudaFree(d_tasks_);
+        cudaFreeHost(h_tasks_);
+        d_tasks_ = nullptr;
+        h_tasks_ = nullptr;
+        tasks_cap_ = std::max(nt, 4096);
+        MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&d_tasks_), sizeof(AttnTask) * tasks_cap_));
+        MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&h_tasks_), sizeof(AttnTask) * tasks_cap_, cudaHostAllocDefault));
+    }
+    MKKV_CK(cudaEventSynchronize(ev_compute_)); // the previous call's upload has been consumed
+    if (nt) memcpy(h_tasks_, tasks.data(), sizeof(AttnTask) * nt);
+    if (nt) MKKV_CK(cudaMemcpyAsync(d_tasks_, h_tasks_, sizeof(AttnTask) * nt, cudaMemcpyHostToDevice, stream_));
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(launch_attend_fast(d_jobs_, &j, 1, NKV * j.nch, T, num_sms_, part_, ml_, work_items_, xmax_, XCH_NB, ++epoch_, d_status_, nullptr, true,
+                               stream_, d_tasks_, nt, B, static_cast<float *>(part_out), static_cast<float2 *>(ml_out)));
+    launches_ += 2;
+}
+
+void KvEngine::combine(int layer, int T, int nparts, const void * parts, const void * mls, void * O) {
+    use_device();
+    check_layer(layer);
+    if (T < 1 || T > MAXT || nparts < 1 || nparts > 64 || !parts || !mls || !O) throw std::runtime_error("combine: bad arguments");
+    AttnJob j;
+    j.kv = main_.views[layer]; // (only the V rotation flag is read)
+    j.Q = nullptr;
+    j.O = static_cast<float *>(O);
+    j.n = 0;
+    j.T = T;
+    j.nch = nparts;
+    j.cs = 0;
+    j.ws = 0;
+    j.item0 = 0;
+    j.pos_lo = j.pos_hi = 0;
+    j.pstride = NKV; // partial p of kv head g is slot p * 4 + g
+    MKKV_CK(launch_merge(nullptr, &j, 1, T, const_cast<float *>(static_cast<const float *>(parts)),
+                         const_cast<float2 *>(static_cast<const float2 *>(mls)), stream_));
+    launches_ += 1;
 }
 
 void KvEngine::attend_static(int seq, int layer, int n, int T, const void * Q, void * O) {
@@ -464,6 +553,9 @@ void KvEngine::attend_static(int seq, int layer, int n, int T, const void * Q, v
     attn_dims(n + T, j.nch, j.cs);
     j.ws = kv_ws(n + T, cfg_.win);
     j.item0 = 0;
+    j.pos_lo = 0;
+    j.pos_hi = n + T;
+    j.pstride = 1;
     if (NKV * j.nch > STATIC_ITEMS)
         throw std::runtime_error("attend_static: the call needs " + std::to_string(NKV * j.nch) + " partial items, the fixed scratch holds " + std::to_string(STATIC_ITEMS));
     spill_to(s, layer, j.ws);
@@ -499,6 +591,9 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
         attn_dims(n[j] + T[j], a.nch, a.cs);
         a.ws = kv_ws(n[j] + T[j], cfg_.win);
         a.item0 = items;
+        a.pos_lo = 0;
+        a.pos_hi = n[j] + T[j];
+        a.pstride = 1;
         items += NKV * a.nch;
         maxT = std::max(maxT, T[j]);
         aj[j].kv = a.kv;
@@ -1072,10 +1167,10 @@ int KvEngine::read_row(int seq, int layer, int side, int g, int pos, bool ring, 
         MKKV_CK(cudaMemcpy(sc, sd.rsc + ((size_t) g * rc_ + pos) * 8, SCALE_ROW, cudaMemcpyDeviceToHost));
         return HD;
     }
-    if (pos < 0 || pos >= s.ctxp) throw std::runtime_error("read_row: position out of range");
-    const size_t rb = row_bytes(sd.bits);
-    MKKV_CK(cudaMemcpy(val, sd.val + ((size_t) g * s.ctxp + pos) * rb, rb, cudaMemcpyDeviceToHost));
-    MKKV_CK(cudaMemcpy(sc, sd.sc + ((size_t) g * s.ctxp + pos) * 8, SCALE_ROW, cudaMemcpyDeviceToHost));
+    if (pos < s.base || pos - s.base >= s.ctxp) throw std::runtime_error("read_row: position out of range");
+    const size_t rb = row_bytes(sd.bits), row = (size_t) g * s.ctxp + (pos - s.base);
+    MKKV_CK(cudaMemcpy(val, sd.val + row * rb, rb, cudaMemcpyDeviceToHost));
+    MKKV_CK(cudaMemcpy(sc, sd.sc + row * 8, SCALE_ROW, cudaMemcpyDeviceToHost));
     return (int) rb;
 }
 
@@ -1092,10 +1187,10 @@ void KvEngine::write_row(int seq, int layer, int side, int g, int pos, bool ring
         MKKV_CK(cudaMemcpy(sd.rsc + ((size_t) g * rc_ + pos) * 8, sc, SCALE_ROW, cudaMemcpyHostToDevice));
         return;
     }
-    if (pos < 0 || pos >= s.ctxp) throw std::runtime_error("write_row: position out of range");
-    const size_t rb = row_bytes(sd.bits);
-    MKKV_CK(cudaMemcpy(sd.val + ((size_t) g * s.ctxp + pos) * rb, val, rb, cudaMemcpyHostToDevice));
-    MKKV_CK(cudaMemcpy(sd.sc + ((size_t) g * s.ctxp + pos) * 8, sc, SCALE_ROW, cudaMemcpyHostToDevice));
+    if (pos < s.base || pos - s.base >= s.ctxp) throw std::runtime_error("write_row: position out of range");
+    const size_t rb = row_bytes(sd.bits), row = (size_t) g * s.ctxp + (pos - s.base);
+    MKKV_CK(cudaMemcpy(sd.val + row * rb, val, rb, cudaMemcpyHostToDevice));
+    MKKV_CK(cudaMemcpy(sd.sc + row * 8, sc, SCALE_ROW, cudaMemcpyHostToDevice));
     s.kv_top = std::max(s.kv_top, pos + 1);
 }
 

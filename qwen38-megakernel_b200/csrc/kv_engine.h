@@ -76,6 +76,15 @@ class KvEngine {
     // ---- the hot path ----
     void append(int seq, int layer, int pos0, int n, const void * K, const void * V);
     void attend(int seq, int layer, int n, int T, const void * Q, void * O);
+    // ---- one sequence split by position over several GPUs ----
+    // This engine's copy of the sequence holds positions [base, base + ctx) (set while the sequence is empty; base a multiple of 32).
+    void set_base(int seq, int base);
+    // Attention of the T tokens at n over positions [pos_lo, pos_hi) only (inside this engine's rows; pos_lo a multiple of 32).
+    // part_out [4][48][256] fp32, ml_out [4][48] (m, l): the un-normalised result per kv head, row (head % 6) T + t.
+    void attend_partial(int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out);
+    // Merge of nparts such partials laid one after another (e.g. after an all-gather): O fp32 [T][24][256], normalised, rotated
+    // back when the layer's V is stored rotated.
+    void combine(int layer, int T, int nparts, const void * parts, const void * mls, void * O);
     // attend() with the split partials in the library's fixed device array: this call allocates nothing
     void attend_static(int seq, int layer, int n, int T, const void * Q, void * O);
     // one launch sequence for several sequences: job j appends T[j] rows at n[j] and attends; packed device buffers in job order
@@ -138,7 +147,7 @@ class KvEngine {
         KvView * d_views = nullptr;
         std::vector<CopyRegion> regions; // snapshot stream order
         CopyRegion * d_regions = nullptr;
-        int n = 0, kv_top = 0;
+        int n = 0, kv_top = 0, base = 0;
         std::vector<int> spilled; // per layer: main rows of ring sides exist for positions < spilled
         std::vector<Checkpoint> cks;
         cudaEvent_t copy_done = nullptr; // set while side-stream copies of this sequence are in flight
@@ -197,6 +206,9 @@ class KvEngine {
     void * d_ajobs_ = nullptr;   // batched append jobs
     void * h_ajobs_ = nullptr;
     int work_jobs_ = 0;
+    AttnTask * d_tasks_ = nullptr; // task list of a position-range job
+    AttnTask * h_tasks_ = nullptr; // pinned
+    int tasks_cap_ = 0;
     int * h_status_ = nullptr; // mapped pinned word the kernels write
     int * d_status_ = nullptr;
     // fast attention path: exchange of row maxima between the CTAs of one chunk

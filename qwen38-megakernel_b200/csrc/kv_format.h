@@ -65,6 +65,8 @@ struct KvView {
     int win;     // MK_KV_WIN
     int eager;   // 1: every appended row is also stored in its main format at once (the reference's state);
                  // 0: main rows are written when a position leaves the window (spill from the fp16 shadow)
+    int base;    // position of main-buffer row 0 (0 unless the sequence is split by position over several GPUs); ring rows
+                 // are always indexed by the global position
 };
 
 // one decode-attention job: T query tokens at positions n .. n + T - 1 of one (sequence, layer)
@@ -75,6 +77,16 @@ struct AttnJob {
     int n, T;
     int nch, cs, ws;    // partition and window start of L = n + T
     int item0;          // first (kv head, chunk) item of this job in the call's partial buffers
+    int pos_lo, pos_hi; // only positions in [pos_lo, pos_hi) are attended (multiples of 32 or the context end; whole context: 0, n + T)
+    int pstride;        // merge: partial c of kv head g is slot item0 + g nch + c (pstride 1), else item0 + c pstride + g
+};
+
+// one batch of tiles of one chunk, as the fast attention kernel runs it (built on the host for position-range jobs)
+struct AttnTask {
+    int c, b, nb; // chunk, batch, batches of the chunk
+    int pos0;     // position of the batch's first tile
+    int c1;       // end of the chunk (clipped to the job's range)
+    int nt;       // tiles of the batch
 };
 
 } // namespace mkkv

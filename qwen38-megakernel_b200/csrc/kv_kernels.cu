@@ -95,7 +95,7 @@ __device__ __forceinline__ void append_row(const KvView & kv, int w, int g, int 
     }
     if (s.rot) fwht256(v, lane);
     if (kv.eager || !s.rval) {
-        const size_t row = (size_t) g * kv.ctxp + pos;
+        const size_t row = (size_t) g * kv.ctxp + (pos - kv.base);
         store_row(s.val + row * row_bytes(s.bits), s.sc + row * 8, v, s.bits, lane);
     }
     if (s.rval) { // the ring keeps the same (rotated) values as q8_0: every tile of a side shares one basis
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) spill_kernel(const KvView * views, int la
         float v[8];
         load_row_f16(s.shadow + ((size_t) g * kv.rc + pos % kv.rc) * HD, lane, v);
         if (s.rot) fwht256(v, lane);
-        const size_t row = (size_t) g * kv.ctxp + pos;
+        const size_t row = (size_t) g * kv.ctxp + (pos - kv.base);
         store_row(s.val + row * row_bytes(s.bits), s.sc + row * 8, v, s.bits, lane);
     }
 }
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(256) refill_kernel(const KvView * views, int l
         const KvView & kv = views[l];
         const KvSide & s = kv.s[w];
         if (!s.rval) continue;
-        const size_t row = (size_t) g * kv.ctxp + pos;
+        const size_t row = (size_t) g * kv.ctxp + (pos - kv.base);
         int q[8];
         row_ints(s.val + row * row_bytes(s.bits), s.bits, lane, q);
         const float d = __half2float(__ushort_as_half(s.sc[row * 8 + (lane >> 2)]));
@@ -285,7 +285,7 @@ __device__ __forceinline__ int tile_src(const KvView & kv, int w, int g, int tb,
         sc = s.rsc + rr * 8;
         return 8;
     }
-    const size_t row = (size_t) g * kv.ctxp + tb;
+    const size_t row = (size_t) g * kv.ctxp + (tb - kv.base);
     val = s.val + row * row_bytes(s.bits);
     sc = s.sc + row * 8;
     return s.bits;
@@ -478,17 +478,21 @@ __global__ void __launch_bounds__(A_THREADS, 1) attn_split_kernel(const __grid_c
 
 // merge of the chunk partials of one (query head, token): y = sum_c w_c O_c / sum_c w_c l_c, w_c = exp(m_c - max m), then the
 // inverse rotation when V is stored rotated (qwen38_mk.cu:4658-4685). One warp per row; lane holds dims 8 lane .. 8 lane + 7.
-__global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__ AttnArgs a, int rows_per_job) {
+// raw != 0: write the merged but un-normalised (m, l, O) of the row instead, as one partial per kv head (slot g of part_out /
+// ml_out, row (head % 6) T + t): the input of a later merge across GPUs
+__global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__ AttnArgs a, int rows_per_job, int raw, float * part_out,
+                                                         float2 * ml_out) {
     const int lane = threadIdx.x & 31, idx = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int j = idx / rows_per_job, rr = idx % rows_per_job;
     if (j >= (a.jobs ? a.njobs : 1)) return;
     const AttnJob & J = a.jobs ? a.jobs[j] : a.one;
     if (rr >= NH * J.T) return;
     const int h = rr / J.T, t = rr % J.T, g = h / GQ, r = (h % GQ) * J.T + t;
-    const size_t i0 = (size_t) J.item0 + (size_t) g * J.nch;
+    const size_t i0 = (size_t) J.item0 + (J.pstride > 1 ? (size_t) g : (size_t) g * J.nch);
+    const size_t cstep = J.pstride > 1 ? (size_t) J.pstride : 1; // slots between consecutive partials of the kv head
     // lane c (and c + 32) holds partial c's (m, l): all weights first, so the sums below run over independent loads
-    float2 mla = lane < J.nch ? a.ml[(i0 + lane) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
-    float2 mlb = lane + 32 < J.nch ? a.ml[(i0 + lane + 32) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
+    float2 mla = lane < J.nch ? a.ml[(i0 + lane * cstep) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
+    float2 mlb = lane + 32 < J.nch ? a.ml[(i0 + (lane + 32) * cstep) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
     float M = fmaxf(mla.x, mlb.x);
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) M = fmaxf(M, __shfl_xor_sync(FULL, M, m));
@@ -500,7 +504,7 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__
 #pragma unroll 4
     for (int c = 0; c < J.nch; c++) { // (partials beyond 64 per kv head do not occur: nch <= 20, or #SM / 4 for the fast path)
         const float w = __shfl_sync(FULL, c < 32 ? wa : wb, c & 31), lc = __shfl_sync(FULL, c < 32 ? mla.y : mlb.y, c & 31);
-        const float4 * o = reinterpret_cast<const float4 *>(pbase + (size_t) c * AR * HD);
+        const float4 * o = reinterpret_cast<const float4 *>(pbase + (size_t) c * cstep * AR * HD);
         const float4 o0 = __ldcg(o), o1 = __ldcg(o + 1);
         num[0] = __fmaf_rn(w, o0.x, num[0]);
         num[1] = __fmaf_rn(w, o0.y, num[1]);
@@ -511,6 +515,13 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__
         num[6] = __fmaf_rn(w, o1.z, num[6]);
         num[7] = __fmaf_rn(w, o1.w, num[7]);
         den = __fmaf_rn(w, lc, den);
+    }
+    if (raw) {
+        float4 * dst = reinterpret_cast<float4 *>(part_out + ((size_t) g * AR + r) * HD + lane * 8);
+        dst[0] = make_float4(num[0], num[1], num[2], num[3]);
+        dst[1] = make_float4(num[4], num[5], num[6], num[7]);
+        if (lane == 0) ml_out[(size_t) g * AR + r] = make_float2(M, den);
+        return;
     }
     float y[8];
 #pragma unroll
@@ -543,12 +554,12 @@ cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, i
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const int rows_per_job = NH * max_T;
-    attn_merge_kernel<<<(njobs * rows_per_job + 7) / 8, 256, 0, stream>>>(a, rows_per_job);
+    attn_merge_kernel<<<(njobs * rows_per_job + 7) / 8, 256, 0, stream>>>(a, rows_per_job, 0, nullptr, nullptr);
     return cudaGetLastError();
 }
 
 cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, float * raw_part, float2 * raw_ml) {
     AttnArgs a;
     a.one = jobs_host[0];
     a.jobs = njobs > 1 ? jobs_dev : nullptr;
@@ -557,7 +568,7 @@ cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, in
     a.ml = ml;
     a.status = nullptr;
     const int rows_per_job = NH * max_T;
-    attn_merge_kernel<<<(njobs * rows_per_job + 7) / 8, 256, 0, stream>>>(a, rows_per_job);
+    attn_merge_kernel<<<(njobs * rows_per_job + 7) / 8, 256, 0, stream>>>(a, rows_per_job, raw_part ? 1 : 0, raw_part, raw_ml);
     return cudaGetLastError();
 }
 

@@ -3,6 +3,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <vector>
+
 #include "kv_format.h"
 
 namespace mkkv {
@@ -25,15 +27,22 @@ cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, i
                           float2 * ml, int * status, cudaStream_t stream);
 
 // the merge alone: job j's partials are slots item0 + g nch .. + nch - 1 of kv head g
+// raw_part / raw_ml (one job only): write the merged but un-normalised result as one partial per kv head, [4][48][256] floats and
+// [4][48] (m, l), instead of the job's O
 cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,
-                         cudaStream_t stream);
+                         cudaStream_t stream, float * raw_part = nullptr, float2 * raw_ml = nullptr);
 // Fast path (kv_attend_fast.cu): same result as launch_attend. One job: cooperative launch over num_sms CTAs with an
 // exchange of row maxima through xmax ([4][20][nbmax][48] 8-byte words {epoch, value}, zeroed once; epoch must be non-zero and
 // differ from every earlier launch's). Several jobs: one CTA per (job, kv head, chunk). part / ml hold part_slots partials.
 // cudaErrorNotSupported: shape not handled (use launch_attend).
 cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, int num_sms,
                                float * part, float2 * ml, int part_slots, unsigned long long * xmax, int nbmax, int epoch, int * status,
-                               unsigned long long * prof, bool spread, cudaStream_t stream);
+                               unsigned long long * prof, bool spread, cudaStream_t stream, const AttnTask * tasks_dev = nullptr,
+                               int ntasks = 0, int tasks_B = 0, float * raw_part = nullptr, float2 * raw_ml = nullptr);
+// A job restricted to positions [pos_lo, pos_hi) (one sequence split over GPUs): its task list for launch_attend_fast, batch-major;
+// returns the most batches any chunk has. tasks_dev must hold the same list on the device; raw_part / raw_ml receive the job's
+// merged, un-normalised (m, l, O) as one partial per kv head ([4][48][256], [4][48]).
+int build_range_tasks(const AttnJob & J, int B, std::vector<AttnTask> & out);
 size_t attend_fast_smem_bytes();
 // prof (optional, null: off): globaltimer stamps of the first batches of every CTA, [CTA][16][20] words: 0 batch start,
 // 1 K tile arrived, 2 scores done, 3 / 4 before / after the batch barrier, 5 incoming max known, 6 running maxima done,

@@ -47,6 +47,9 @@ def load_library():
         "mk_kv_append": (i, [vp, i, i, i, i, vp, vp]),
         "mk_kv_attend": (i, [vp, i, i, i, i, vp, vp]),
         "mk_kv_attend_static": (i, [vp, i, i, i, i, vp, vp]),
+        "mk_kv_set_base": (i, [vp, i, i]),
+        "mk_kv_attend_partial": (i, [vp, i, i, i, i, vp, i, i, vp, vp]),
+        "mk_kv_combine": (i, [vp, i, i, i, vp, vp, vp]),
         "mk_kv_step": (i, [vp, i, i, i, i, vp, vp, vp, vp]),
         "mk_kv_reserve_batch": (i, [vp, i]),
         "mk_kv_step_batch": (i, [vp, i, ip, i, ip, ip, vp, vp, vp, vp]),
@@ -184,6 +187,19 @@ class Engine:
     def attend_static(self, layer, n, Q, O, seq=SEQ_MAIN):
         """attend() that allocates nothing: partials go to the library's fixed device array (see mk_kv_attend_static)"""
         self._ck(self.L.mk_kv_attend_static(self.h, seq, layer, n, Q.shape[0], _ptr(Q), _ptr(O)), "attend_static")
+
+    def set_base(self, base, seq=SEQ_MAIN):
+        """this engine's copy of the sequence holds positions [base, base + ctx) (a sequence split by position over GPUs)"""
+        self._ck(self.L.mk_kv_set_base(self.h, seq, base), "set_base")
+
+    def attend_partial(self, layer, n, Q, pos_lo, pos_hi, part_out, ml_out, seq=SEQ_MAIN):
+        """un-normalised attention of the T tokens at n over positions [pos_lo, pos_hi): part_out [4][48][256], ml_out [4][48][2]"""
+        self._ck(self.L.mk_kv_attend_partial(self.h, seq, layer, n, Q.shape[0], _ptr(Q), pos_lo, pos_hi, _ptr(part_out), _ptr(ml_out)),
+                 "attend_partial")
+
+    def combine(self, layer, T, nparts, parts, mls, O):
+        """merge of nparts partial results (all-gathered) into O [T][24][256]"""
+        self._ck(self.L.mk_kv_combine(self.h, layer, T, nparts, _ptr(parts), _ptr(mls), _ptr(O)), "combine")
 
     def step(self, layer, n, K, V, Q, O, seq=SEQ_MAIN):
         self._ck(self.L.mk_kv_step(self.h, seq, layer, n, Q.shape[0], _ptr(K), _ptr(V), _ptr(Q), _ptr(O)), "step")
