@@ -45,7 +45,7 @@ void cuda_fail(cudaError_t e, const char * what, const char * file, int line) {
     throw MKCudaError(msg);
 }
 
-constexpr int XCH_NB = 64; // batches per chunk the exchange arrays of the fast attention kernel hold
+constexpr int XCH_NB_MIN = 64; // fewest batches per chunk the exchange arrays of the spread attention kernels hold
 
 namespace {
 bool parse_spec(const std::string & str, int layers, int (*kvb)[MAX_LAYERS], int (*rot)[MAX_LAYERS]) {
@@ -110,10 +110,12 @@ KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
         if (v >= 1 && v <= 1024) hs_chunk_ = (size_t) v << 20;
     }
     MKKV_CK(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, dev_));
-    if (const char * c = getenv("MK_KV_ATTN")) use_fast_ = strcmp(c, "baseline") != 0; // "baseline": the simple kernel only
-    constexpr size_t XN = (size_t) NKV * ATT_NCH * XCH_NB;
-    MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&xmax_), XN * AR * sizeof(unsigned long long)));
-    MKKV_CK(cudaMemset(xmax_, 0, XN * AR * sizeof(unsigned long long)));
+    // MK_KV_ATTN: "tc" (default: tensor-core kernel, the others as fallbacks), "fast" (no tcgen05 kernel), "baseline" (the simple kernel only)
+    if (const char * c = getenv("MK_KV_ATTN")) {
+        use_fast_ = strcmp(c, "baseline") != 0;
+        use_tc_ = strcmp(c, "baseline") != 0 && strcmp(c, "fast") != 0;
+    }
+    ensure_xch(((cfg.ctx + ATT_BUCKET - 1) / ATT_BUCKET + 3) / 4 + 2);
     if (const char * c = getenv("MK_KV_PROFILE"))
         if (atoi(c) > 0) {
             MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&prof_), attend_fast_prof_words(num_sms_) * sizeof(unsigned long long)));
@@ -123,11 +125,36 @@ KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
     ensure_work(std::max(NKV * ATT_NCH, num_sms_), 1);
 }
 
-// the decode-attention launches of one call: the fast kernel, or the baseline one for shapes it does not take
+// exchange arrays of the spread attention kernels: two of [4][20][nb][48] words (zeroed: no word carries a launch tag yet)
+void KvEngine::ensure_xch(int nb) {
+    if (nb <= xnb_) return;
+    nb = std::max(nb, XCH_NB_MIN);
+    if (xmax_) {
+        MKKV_CK(cudaStreamSynchronize(stream_));
+        MKKV_CK(cudaFree(xmax_));
+        xmax_ = nullptr;
+    }
+    const size_t words = 2 * (size_t) NKV * ATT_NCH * nb * AR;
+    MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&xmax_), words * sizeof(unsigned long long)));
+    MKKV_CK(cudaMemset(xmax_, 0, words * sizeof(unsigned long long)));
+    xnb_ = nb;
+}
+
+// the decode-attention launches of one call: the tensor-core kernel, the fast one, or the baseline one for shapes those do not take
 void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items, int max_T) {
+    if (use_tc_ && njobs == 1) {
+        const cudaError_t e = launch_attend_tc(jobs_host[0], num_sms_, part_, ml_, work_items_, xmax_, xmax_ + (size_t) NKV * ATT_NCH * xnb_ * AR,
+                                               xnb_, ++epoch_, d_status_, stream_, nullptr, 0, 0, nullptr, nullptr, prof_);
+        if (e == cudaSuccess) {
+            launches_ += 2;
+            return;
+        }
+        if (e != cudaErrorNotSupported && e != cudaErrorCooperativeLaunchTooLarge) MKKV_CK(e);
+        cudaGetLastError();
+    }
     if (use_fast_) {
         const cudaError_t e = launch_attend_fast(d_jobs_, jobs_host, njobs, items, max_T, num_sms_, part_, ml_, work_items_, xmax_,
-                                                 XCH_NB, ++epoch_, d_status_, njobs == 1 ? prof_ : nullptr, true, stream_);
+                                                 std::min(xnb_, 64), ++epoch_, d_status_, njobs == 1 ? prof_ : nullptr, true, stream_);
         if (e == cudaSuccess) {
             launches_ += 2;
             return;
@@ -493,25 +520,37 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
     j.pstride = 1;
     if (pos_hi > pos_lo) spill_to(s, layer, std::min(j.ws, pos_hi)); // rows of this range that left the window
     std::vector<AttnTask> tasks;
-    const int B = 8, max_nb = build_range_tasks(j, B, tasks);
-    if (max_nb > XCH_NB) throw std::runtime_error("attend_partial: the context is too long for the exchange buffers");
-    const int nt = (int) tasks.size();
-    if (nt > tasks_cap_) {
-        MKKV_CK(cudaStreamSynchronize(stream_));
-        cudaFree(d_tasks_);
-        cudaFreeHost(h_tasks_);
-        d_tasks_ = nullptr;
-        h_tasks_ = nullptr;
-        tasks_cap_ = std::max(nt, 4096);
-        MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&d_tasks_), sizeof(AttnTask) * tasks_cap_));
-        MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&h_tasks_), sizeof(AttnTask) * tasks_cap_, cudaHostAllocDefault));
+    bool tc = use_tc_;
+    for (;; tc = false) { // the tensor-core kernel first (4 tiles per task), else the fast kernel (8)
+        const int B = tc ? 4 : 8, max_nb = build_range_tasks(j, B, tasks);
+        if (tc) ensure_xch(max_nb);
+        else if (max_nb > std::min(xnb_, 64)) throw std::runtime_error("attend_partial: the context is too long for the exchange buffers");
+        const int nt = (int) tasks.size();
+        if (nt > tasks_cap_) {
+            MKKV_CK(cudaStreamSynchronize(stream_));
+            cudaFree(d_tasks_);
+            cudaFreeHost(h_tasks_);
+            d_tasks_ = nullptr;
+            h_tasks_ = nullptr;
+            tasks_cap_ = std::max(nt, 4096);
+            MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&d_tasks_), sizeof(AttnTask) * tasks_cap_));
+            MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&h_tasks_), sizeof(AttnTask) * tasks_cap_, cudaHostAllocDefault));
+        }
+        MKKV_CK(cudaEventSynchronize(ev_compute_)); // the previous call's upload has been consumed
+        if (nt) memcpy(h_tasks_, tasks.data(), sizeof(AttnTask) * nt);
+        if (nt) MKKV_CK(cudaMemcpyAsync(d_tasks_, h_tasks_, sizeof(AttnTask) * nt, cudaMemcpyHostToDevice, stream_));
+        MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+        cudaError_t e;
+        if (tc)
+            e = launch_attend_tc(j, num_sms_, part_, ml_, work_items_, xmax_, xmax_ + (size_t) NKV * ATT_NCH * xnb_ * AR, xnb_, ++epoch_, d_status_,
+                                 stream_, d_tasks_, nt, B, static_cast<float *>(part_out), static_cast<float2 *>(ml_out));
+        else
+            e = launch_attend_fast(d_jobs_, &j, 1, NKV * j.nch, T, num_sms_, part_, ml_, work_items_, xmax_, std::min(xnb_, 64), ++epoch_, d_status_,
+                                   nullptr, true, stream_, d_tasks_, nt, B, static_cast<float *>(part_out), static_cast<float2 *>(ml_out));
+        if (e == cudaSuccess) break;
+        if (!tc || (e != cudaErrorNotSupported && e != cudaErrorCooperativeLaunchTooLarge)) MKKV_CK(e);
+        cudaGetLastError();
     }
-    MKKV_CK(cudaEventSynchronize(ev_compute_)); // the previous call's upload has been consumed
-    if (nt) memcpy(h_tasks_, tasks.data(), sizeof(AttnTask) * nt);
-    if (nt) MKKV_CK(cudaMemcpyAsync(d_tasks_, h_tasks_, sizeof(AttnTask) * nt, cudaMemcpyHostToDevice, stream_));
-    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
-    MKKV_CK(launch_attend_fast(d_jobs_, &j, 1, NKV * j.nch, T, num_sms_, part_, ml_, work_items_, xmax_, XCH_NB, ++epoch_, d_status_, nullptr, true,
-                               stream_, d_tasks_, nt, B, static_cast<float *>(part_out), static_cast<float2 *>(ml_out)));
     launches_ += 2;
 }
 

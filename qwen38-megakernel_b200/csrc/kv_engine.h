@@ -214,7 +214,9 @@ class KvEngine {
     // fast attention path: exchange of row maxima between the CTAs of one chunk
     unsigned long long * xmax_ = nullptr;
     int epoch_ = 0, num_sms_ = 0;
-    bool use_fast_ = true;
+    bool use_fast_ = true, use_tc_ = true;
+    int xnb_ = 0; // batches per chunk the exchange arrays hold
+    void ensure_xch(int nb);
     unsigned long long * prof_ = nullptr; // MK_KV_PROFILE=1: phase stamps of the last fast attention launch
     void launch_attention(const AttnJob * jobs_host, int njobs, int items, int max_T);
 

