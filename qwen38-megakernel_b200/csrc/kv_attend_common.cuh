@@ -40,12 +40,9 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 }
 // bounded wait (about two seconds): on expiry the status word is set and the caller goes on, so the kernel always ends
 __device__ __forceinline__ void mbar_wait(uint64_t * bar, unsigned parity, int * status) {
-    if (mbar_try_wait(bar, parity)) return;
-    const unsigned long long t0 = globaltimer_ns();
-    for (unsigned it = 0;; it++) {
-        if (mbar_try_wait(bar, parity)) return;
-        __nanosleep(32);
-        if ((it & 1023u) == 1023u && globaltimer_ns() - t0 > 2000000000ull) {
+    // (a try_wait suspends the thread for a hardware-chosen time before it reports failure: 2^23 rounds are seconds)
+    for (unsigned it = 0; !mbar_try_wait(bar, parity); it++) {
+        if (it >= (1u << 23)) {
             if (status) atomicExch(status, (int) KS_WAIT_TIMEOUT);
             return;
         }

@@ -1,21 +1,21 @@
 // Decode attention on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory) for one sequence spread over
 // every SM. Same arithmetic as the other two attention kernels (the reference's attn_core_t, qwen38_mk.cu:2756-3067): the
-// chunk partition attn_dims, 32-position tiles in order inside a chunk with a running max, P = fp16(expf(S - max)), fp32
-// accumulation. The structure is a dequantising GEMM main loop:
+// chunk partition attn_dims, 32-position tiles in order inside a chunk with a running max, P = fp16(exp(S - max)), fp32
+// accumulation. The structure is a warp-specialised dequantising GEMM main loop:
 //   - the unit of work is a group of 4 consecutive tiles (128 positions) of one chunk; the groups of a kv head are dealt in
 //     group-major order to the CTAs of that head (cooperative launch: all CTAs resident);
 //   - one producer thread streams the packed K / V rows of the CTA's groups into a ring of shared-memory slots with bulk
 //     copies completing on mbarriers;
-//   - 16 worker warps turn packed rows into exact fp16(d * q) operands in the canonical no-swizzle UMMA layouts (one thread:
+//   - 16 unpack warps turn packed rows into exact fp16(d * q) operands in the canonical no-swizzle UMMA layouts (one thread:
 //     one position x 32 dims per step) -- K as the K-major A operand of S^T[128 pos x 48 rows] = K Q^T, V as the MN-major A
 //     operand of O^T[256 dims x 48 rows] += V^T P^T;
-//   - one issuer thread runs tcgen05.mma on the slots as they fill (mbarrier "full" from the workers, tcgen05.commit to
-//     "empty"), S^T double-buffered in tensor memory, O^T (two 128-dim halves) resident there for the whole kernel;
-//   - the workers read S^T back (tcgen05.ld: a thread owns one position and 12 query rows), take the tile maxima, exchange
-//     the running max with the CTAs that hold the chunk's earlier groups through small global arrays (own group maxima and
-//     cumulative maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as the B
-//     operand. The accumulator is kept against a per-row reference max that moves rarely (when the running max passes it by
-//     more than 8): P is multiplied by exp(running max - reference) in fp32 after its fp16 rounding and split into an fp16
+//   - one issuer thread runs tcgen05.mma on the slots as they fill (mbarrier "full" from the unpack warps, tcgen05.commit
+//     to "empty"), S^T triple-buffered in tensor memory, O^T (two 128-dim halves) resident there for the whole kernel;
+//   - 8 softmax warps read S^T back (tcgen05.ld: a thread owns one position and 24 query rows), take the tile maxima,
+//     exchange the running max with the CTAs that hold the chunk's earlier groups through small global arrays (own group
+//     maxima and cumulative maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as
+//     the B operand. The accumulator is kept against a per-row reference max that moves rarely (when the running max passes
+//     it by more than 8): P, after its fp16 rounding, is multiplied by exp(running max - reference) and carried as an fp16
 //     high and low part (two MMAs), so the reference's fp16 P is reproduced and no per-tile accumulator rescale is needed;
 //   - a CTA writes one un-normalised partial (m, l, O); attn_merge_kernel combines them.
 // Every wait is bounded (about two seconds), then the status word is set and the kernel runs to its end and frees its
@@ -34,32 +34,44 @@ namespace tc {
 
 using namespace attn_common;
 
-constexpr int NWORK = 16;                  // worker warps
-constexpr int NTHREADS = (NWORK + 2) * 32; // + the MMA issuer warp + the copy producer warp
-constexpr int GT = 4, GP = GT * ATP;       // tiles / positions per group: the M of one MMA
-constexpr int RS = 12;                     // query rows per worker warp (4 warps share a tile: 48 rows)
+constexpr int NSOFT = 8;   // softmax warps 0 .. 7: warp = 4 c2 + q, tile q (tensor-memory lanes 32 q ..), query rows 24 c2 .. + 23
+constexpr int NDQ = 16;    // unpack warps 8 .. 23: 4 c + q, tile q, dims 32 (4 h + c) .. + 31 of half h
+constexpr int W_ISSUE = NSOFT + NDQ, W_PROD = W_ISSUE + 1;
+constexpr int NTHREADS = (W_PROD + 3) * 32; // two idle warps complete the last group of four (register reallocation is per group)
+constexpr int GT = 4, GP = GT * ATP;        // tiles / positions per group: the M of one MMA
+constexpr int RS = AR / 2;                  // query rows per softmax warp
 constexpr int RAW_SLOT = ATP * HD + ATP * SCALE_ROW; // one tile of the widest format and its scales: 8704 bytes
 constexpr int NRAW = 9;
-constexpr int OP_SLOT = GP * 128 * 2;      // fp16 operand: 128 positions x 128 dims
+constexpr int OP_SLOT = GP * 128 * 2;       // fp16 operand: 128 positions x 128 dims
 constexpr int NOP = 3;
+constexpr int NSB = 3;                      // S^T buffers
 constexpr int Q_BYTES = AR * HD * 2, P_BYTES = AR * GP * 2;
-constexpr unsigned S_COL0 = 0, S_COL1 = 64, O_COL0 = 128, O_COL1 = 192, TMEM_COLS = 256;
-constexpr float REF_SLACK = 8.f; // the accumulator's reference max moves when the running max passes it by more than this
+constexpr unsigned S_COL = 0, S_STRIDE = 64, O_COL0 = 192, O_COL1 = 320, TMEM_COLS = 512; // an O^T half: 48 columns for P's high part, 48 for its low part
+// The accumulator's reference max of a row is set REF_MARGIN above the running max it is taken from and moves when the running max
+// passes it by more than REF_SLACK: exp(running - reference) stays within [e^-3 for the row's largest terms, e^10.5 < fp16 max].
+constexpr float REF_SLACK = 10.5f, REF_MARGIN = 3.f;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct WarpScratch { // what the row-owner lanes of a softmax warp hand to all its lanes
+    float m[RS];     // running max of the warp's tile (+inf where nothing is visible yet: exp2 gives 0)
+    float beta[RS];  // exp(running max - reference max)
+    float f[RS];     // factor of a moved reference max
+    unsigned bh[RS / 2], bl[RS / 2]; // beta as fp16 high + low parts, rows (2 j, 2 j + 1) packed
+};
 
 struct Smem {
     uint8_t op[NOP][OP_SLOT];   // [dim group 16][position group 16][8 positions][8 dims] fp16
     uint8_t raw[NRAW][RAW_SLOT];
     uint8_t q[Q_BYTES];         // [dim group 32][row group 6][8 rows][8 dims]
     uint8_t p[2][P_BYTES];      // high / low part: [row group 6][position group 16][8 positions][8 rows]
-    float tmax[GT][AR];         // row maxima of the group's tiles
-    float mrun[2][GT][AR];      // running max each tile's P is taken against (by group parity, as beta / fsc / resc)
-    float beta[2][GT][AR];      // exp(running max - reference max)
-    float fsc[2][AR];           // factor that brings the accumulator row to a moved reference max
-    float lsum[GT][AR];
-    int resc[2];
+    int tmax[3][GT][AR];        // row maxima of a group's tiles as order-preserving integer keys; by group % 3: a group's maxima are
+                                // read while the next group's are written, and a warp is never two groups ahead of its slice.
+                                // The first buffer holds the row sums at the end.
+    WarpScratch ws[NSOFT];
     unsigned char rtok[AR];     // token of a query row
     unsigned tmem_base;
-    uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[2], s_empty[2], p_full, p_empty;
+    int dead;                   // a wait of this CTA gave up: no later wait blocks
+    uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[NSB], s_empty[NSB], p_full, p_empty;
     AttnJob job;
 };
 
@@ -73,13 +85,43 @@ struct Args {
     unsigned long long * xb; // same shape: row maxima of the chunk up to and including the group
     int nbmax, epoch;
     int * status;
-    unsigned long long * prof; // optional: [CTA][16 groups][20] globaltimer stamps of worker warp 0 (0 .. 15) and the issuer (16 .. 19)
+    unsigned long long * prof; // optional: [CTA][16 groups][20] globaltimer stamps: softmax warp 0 (0 .. 7), unpack warp 8 (8 .. 15),
+                               // issuer (16 .. 19)
 };
 #define TC_STAMP(grp, k)                                                                                               \
     do {                                                                                                               \
-        if (a.prof && lane == 0 && (warp == 0 || warp == NWORK) && (grp) < 16)                                         \
+        if (a.prof && lane == 0 && (grp) >= 0 && (grp) < 16)                                                           \
             a.prof[((size_t) blockIdx.x * 16 + (grp)) * 20 + (k)] = globaltimer_ns();                                  \
     } while (0)
+
+// Wait for a phase of an mbarrier. A failed try suspends the thread in hardware for up to the hinted time (it wakes when the phase
+// completes), so waiting warps take next to no issue slots. Bounded: after WAIT_ROUNDS failed tries the status word and the CTA's
+// `dead` flag are set; from then on no wait of this CTA blocks, and the kernel runs to its end.
+#ifndef MKKV_WAIT_HINT_NS
+#define MKKV_WAIT_HINT_NS 10000
+#endif
+constexpr unsigned WAIT_HINT_NS = MKKV_WAIT_HINT_NS, WAIT_ROUNDS = 200000u;
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t * bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tc_wait(uint64_t * bar, unsigned parity, volatile int * dead, int * status) {
+    for (unsigned it = 0; !mbar_try_wait_hint(bar, parity); it++) {
+        if (*dead) return;
+        if (it >= WAIT_ROUNDS) {
+            *dead = 1;
+            atomicExch(status, (int) KS_WAIT_TIMEOUT);
+            return;
+        }
+    }
+}
 
 // ---- tcgen05 ----
 __device__ __forceinline__ uint64_t smem_desc(unsigned addr, unsigned lbo, unsigned sbo) { // no swizzle, version 1
@@ -87,37 +129,93 @@ __device__ __forceinline__ uint64_t smem_desc(unsigned addr, unsigned lbo, unsig
 }
 // D[128 x 48] (+)= A B, fp16 operands, fp32 accumulate; MN: both operands MN-major, else both K-major
 constexpr unsigned IDESC_K = (1u << 4) | ((unsigned) (AR / 8) << 17) | ((unsigned) (GP / 16) << 24);
-constexpr unsigned IDESC_MN = IDESC_K | (1u << 15) | (1u << 16);
-__device__ __forceinline__ void umma(unsigned d_tmem, uint64_t da, uint64_t db, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-                 "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-                 : "memory");
+constexpr unsigned IDESC_MN = (1u << 4) | (1u << 15) | (1u << 16) | ((unsigned) (2 * AR / 8) << 17) | ((unsigned) (GP / 16) << 24); // N = 96
+// (descriptors as their 32-bit halves: only the low half, which holds the start address, changes between k-steps)
+__device__ __forceinline__ void umma(unsigned d_tmem, unsigned a_lo, unsigned a_hi, unsigned b_lo, unsigned b_hi, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
+__device__ __forceinline__ unsigned desc_lo(unsigned addr, unsigned lbo) { return ((addr >> 4) & 0x3fffu) | (((lbo >> 4) & 0x3fffu) << 16); }
+__device__ __forceinline__ unsigned desc_hi(unsigned sbo) { return ((sbo >> 4) & 0x3fffu) | (1u << 14); }
 __device__ __forceinline__ void umma_commit(uint64_t * bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// 12 consecutive columns of the warp's 32 lanes (thread: lane, 12 values)
-__device__ __forceinline__ void tmem_ld12(unsigned taddr, float (&v)[RS]) {
+// 24 consecutive columns of the warp's 32 lanes (thread: lane, 24 values)
+__device__ __forceinline__ void tmem_ld24(unsigned taddr, float (&v)[RS]) {
     unsigned r[RS];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr));
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]) : "r"(taddr + 8));
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23])
+                 : "r"(taddr + 16));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < RS; i++) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tmem_st12(unsigned taddr, const float (&v)[RS]) {
+// 8 consecutive columns, in flight until tmem_wait8 on the same registers (the wait names them so that no use can move above it)
+__device__ __forceinline__ void tmem_ld8_async(unsigned taddr, unsigned (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait8(unsigned (&r)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])::"memory");
+}
+// 8 consecutive columns
+__device__ __forceinline__ void tmem_ld8(unsigned taddr, float (&v)[8]) {
+    unsigned r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st8(unsigned taddr, const float (&v)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(__float_as_uint(v[0])),
                  "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])),
                  "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7]))
                  : "memory");
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr + 8), "r"(__float_as_uint(v[8])),
-                 "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11]))
+}
+__device__ __forceinline__ void tmem_st24(unsigned taddr, const float (&v)[RS]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+                 "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                 "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                 "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                 "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
                  : "memory");
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr + 16), "r"(__float_as_uint(v[16])),
+                 "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+                 "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23]))
+                 : "memory");
+}
+#ifndef MKKV_TC_EXPF
+#define MKKV_TC_EXPF 0 // 1: P through expf instead of ex2.approx (experiments)
+#endif
+// exp(x), relative error about 2^-21 (scale factors applied alike to the accumulator and the row sums)
+__device__ __forceinline__ float exp_any(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(__fmul_rn(x, LOG2E)));
+    return y;
+}
+// exp(x) for x <= 0 (and -inf -> 0)
+__device__ __forceinline__ float exp_neg(float x) {
+#if MKKV_TC_EXPF
+    return expf(x);
+#else
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(__fmul_rn(x, LOG2E)));
+    return y;
+#endif
 }
 
 // ---- one worker step: position `row` of a staged tile, dims 32 jb .. 32 jb + 31 -> four 16-byte operand units ----
@@ -181,18 +279,39 @@ __device__ __forceinline__ float key2f(int k) { return __int_as_float(k ^ ((k >>
 
 // bounded poll of an exchange word until it carries this launch's tag
 __device__ __forceinline__ float poll_word(const unsigned long long * src, unsigned long long w, int epoch, int * status) {
-    if ((unsigned) (w >> 32) != (unsigned) epoch) {
-        const unsigned long long t0 = globaltimer_ns();
-        for (unsigned it = 0;; it++) {
-            w = __ldcv(src);
-            if ((unsigned) (w >> 32) == (unsigned) epoch) break;
-            if ((it & 255u) == 255u && globaltimer_ns() - t0 > 2000000000ull) {
-                atomicExch(status, (int) KS_WAIT_TIMEOUT);
-                break;
-            }
+    for (unsigned it = 0; (unsigned) (w >> 32) != (unsigned) epoch; it++) {
+        if (it >= (1u << 21)) { // (a round is a trip to the L2: seconds)
+            atomicExch(status, (int) KS_WAIT_TIMEOUT);
+            break;
         }
+        w = __ldcv(src);
     }
     return __uint_as_float((unsigned) w);
+}
+// task t of a kv head (group-major over its chunks), 4 tiles per task; mul_*: ceil(2^32 / divisor) (exact quotients for t < 2^26)
+struct Geo4 {
+    Geo g;
+    unsigned mul_nch, mul_nch1;
+};
+__device__ __forceinline__ Task make_task4(const Geo4 & G4, int t) {
+    const Geo & g = G4.g;
+    Task k;
+    const int first = g.nb_last * g.nch;
+    if (t < first) {
+        k.b = g.nch > 1 ? (int) __umulhi((unsigned) t, G4.mul_nch) : t;
+        k.c = t - k.b * g.nch;
+    } else {
+        const int u = t - first;
+        const int qd = g.nch > 2 ? (int) __umulhi((unsigned) u, G4.mul_nch1) : u;
+        k.b = g.nb_last + qd;
+        k.c = u - qd * (g.nch - 1);
+    }
+    const int ntc = k.c == g.nch - 1 ? g.nt_last : g.nt_full;
+    k.nb = (ntc + GT - 1) / GT;
+    k.c1 = min(g.L, (k.c + 1) * g.cs);
+    k.pos0 = k.c * g.cs + k.b * GP;
+    k.nt = min(GT, ntc - k.b * GT);
+    return k;
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_constant__ Args a) {
@@ -205,15 +324,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         for (int i = tid; i < (int) (sizeof(AttnJob) / 4); i += NTHREADS) dst[i] = src[i];
     }
     if (tid == 0) {
-        for (int s = 0; s < NRAW; s++) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], NWORK / GT); }
-        for (int s = 0; s < NOP; s++) { mbar_init(&sm.op_full[s], NWORK); mbar_init(&sm.op_empty[s], 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(&sm.s_full[s], 1); mbar_init(&sm.s_empty[s], NWORK); }
-        mbar_init(&sm.p_full, NWORK);
+        for (int s = 0; s < NRAW; s++) { mbar_init(&sm.raw_full[s], 1); mbar_init(&sm.raw_empty[s], NDQ / GT); }
+        for (int s = 0; s < NOP; s++) { mbar_init(&sm.op_full[s], NDQ); mbar_init(&sm.op_empty[s], 1); }
+        for (int s = 0; s < NSB; s++) { mbar_init(&sm.s_full[s], 1); mbar_init(&sm.s_empty[s], NSOFT); }
+        mbar_init(&sm.p_full, NSOFT);
         mbar_init(&sm.p_empty, 1);
-        sm.resc[0] = sm.resc[1] = 0;
+        sm.dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == NWORK) { // tensor memory: S^T twice, O^T in two halves
+    if (warp == W_ISSUE) { // tensor memory: S^T three times, O^T in two halves
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -222,10 +341,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
     const KvView & kv = J.kv;
     const int g = blockIdx.x / a.cph, kk = blockIdx.x % a.cph, slot = blockIdx.x;
     const int T = J.T, n = J.n, R = GQ * T, ws = J.ws;
-    const Geo geo = make_geo(J, GT);
+    Geo4 geo4;
+    geo4.g = make_geo(J, GT);
+    geo4.mul_nch = geo4.g.nch > 1 ? 0xffffffffu / (unsigned) geo4.g.nch + 1u : 0u;
+    geo4.mul_nch1 = geo4.g.nch > 2 ? 0xffffffffu / (unsigned) (geo4.g.nch - 1) + 1u : 0u;
     const AttnTask * const ttab = a.tasks;
-    const int t_end = ttab ? a.ntasks : geo.ntasks_head;
-    auto get_task = [&](int t) -> Task { return ttab ? ttab[t] : make_task(geo, GT, 0, t, 0); };
+    const int t_end = ttab ? a.ntasks : geo4.g.ntasks_head;
+    auto get_task = [&](int t) -> Task { return ttab ? ttab[t] : make_task4(geo4, t); };
     const int G = kk < t_end ? (t_end - kk + a.cph - 1) / a.cph : 0; // this CTA's groups: tasks kk, kk + cph, ..
 
     // query rows of the kv head: fp16 -> fp32 -> (K's rotation) -> x 1/16 -> fp16 (qwen38_mk.cu:2876-2883), row = (head % 6) T + t,
@@ -255,163 +377,203 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const unsigned tb = sm.tmem_base;
-
-    if (warp == NWORK + 1) {
-        // ---- producer: K(0), K(1), then V(i), K(i + 2) -- the order the workers consume ----
+    // registers move from the unpack / control warps to the softmax warps (72 each at launch)
+    if (warp >= NSOFT) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == W_PROD) {
+        // ---- producer: K(0), K(1), K(2), then V(i), K(i + 3) -- the order the unpack warps consume ----
         if (lane == 0) {
             const SideSrc ksrc = make_src(kv, 0, g, ws), vsrc = make_src(kv, 1, g, ws);
             unsigned rseq = 0;
-            auto load_unit = [&](const SideSrc & S, int i) {
-                const Task k = get_task(kk + i * a.cph);
+            for (int nk = 0, nv = 0; nv < G;) { // K runs NSB groups ahead of V
+                const bool isK = nk < G && nk < nv + NSB;
+                const Task k = get_task(kk + (isK ? nk : nv) * a.cph);
+                const SideSrc & S = isK ? ksrc : vsrc;
                 for (int qq = 0; qq < GT; qq++, rseq++) {
                     const int rs = rseq % NRAW;
                     const unsigned round = rseq / NRAW;
-                    if (round > 0) mbar_wait(&sm.raw_empty[rs], (round - 1) & 1, a.status);
+                    if (round > 0) tc_wait(&sm.raw_empty[rs], (round - 1) & 1, &sm.dead, a.status);
                     if (qq < k.nt) issue_tile(S, k.pos0 + qq * ATP, k.c1, sm.raw[rs], &sm.raw_full[rs]);
                     else mbar_arrive(&sm.raw_full[rs]);
                 }
-            };
-            if (G > 0) load_unit(ksrc, 0);
-            if (G > 1) load_unit(ksrc, 1);
-            for (int i = 0; i < G; i++) {
-                load_unit(vsrc, i);
-                if (i + 2 < G) load_unit(ksrc, i + 2);
+                if (isK) nk++;
+                else nv++;
             }
         }
-    } else if (warp == NWORK) {
-        // ---- issuer: S(0), S(1), then PV(i), S(i + 2) ----
+    } else if (warp == W_ISSUE) {
+        // ---- issuer: S(0), S(1), S(2), then PV(i), S(i + 3) ----
         if (lane == 0) {
             unsigned oseq = 0;
-            const unsigned qaddr = smem_u32(sm.q), phi = smem_u32(sm.p[0]), plo = smem_u32(sm.p[1]);
-            auto do_S = [&](int j) {
-                if (j >= 2) mbar_wait(&sm.s_empty[j & 1], ((j >> 1) - 1) & 1, a.status);
-                const unsigned dcol = tb + ((j & 1) ? S_COL1 : S_COL0);
-                for (int h = 0; h < 2; h++, oseq++) {
-                    const int os = oseq % NOP;
-                    mbar_wait(&sm.op_full[os], (oseq / NOP) & 1, a.status);
-                    tc_fence_after();
-                    const unsigned ab = smem_u32(sm.op[os]);
+            const unsigned q_lo = desc_lo(smem_u32(sm.q), AR / 8 * 128), p_lo0 = desc_lo(smem_u32(sm.p[0]), 128);
+            const unsigned hi_k = desc_hi(128), hi_mn = desc_hi(2048); // K-major: 8-row groups 128 bytes apart; MN-major: 2048
+            for (int nk = 0, nv = 0; nv < G;) {
+                const bool isK = nk < G && nk < nv + NSB;
+                if (isK) { // S^T(nk) = K Q^T
+                    const int sb = nk % NSB;
+                    if (nk >= NSB) tc_wait(&sm.s_empty[sb], ((nk / NSB) - 1) & 1, &sm.dead, a.status);
+                    const unsigned dcol = tb + S_COL + S_STRIDE * sb;
+#pragma unroll 1
+                    for (int h = 0; h < 2; h++, oseq++) {
+                        const int os = oseq % NOP;
+                        tc_wait(&sm.op_full[os], (oseq / NOP) & 1, &sm.dead, a.status);
+                        tc_fence_after();
+                        const unsigned a_lo = desc_lo(smem_u32(sm.op[os]), 2048), b_lo = q_lo + ((8 * h) * (2 * AR / 8 * 128) >> 4);
 #pragma unroll
-                    for (int ks = 0; ks < 8; ks++)
-                        umma(dcol, smem_desc(ab + ks * 4096, 2048, 128), smem_desc(qaddr + (8 * h + ks) * (2 * AR / 8 * 128), AR / 8 * 128, 128), IDESC_K,
-                             (unsigned) (h | ks));
-                    umma_commit(&sm.op_empty[os]);
-                }
-                umma_commit(&sm.s_full[j & 1]);
-            };
-            auto do_PV = [&](int i) {
-                TC_STAMP(i, 16);
-                mbar_wait(&sm.p_full, i & 1, a.status);
-                TC_STAMP(i, 17);
-                for (int h = 0; h < 2; h++, oseq++) {
-                    const int os = oseq % NOP;
-                    mbar_wait(&sm.op_full[os], (oseq / NOP) & 1, a.status);
-                    if (h == 0) TC_STAMP(i, 18);
-                    tc_fence_after();
-                    const unsigned ab = smem_u32(sm.op[os]), dcol = tb + (h ? O_COL1 : O_COL0);
-#pragma unroll
-                    for (int ks = 0; ks < 8; ks++) {
-                        const uint64_t da = smem_desc(ab + ks * 256, 128, 2048);
-                        umma(dcol, da, smem_desc(phi + ks * 256, 128, 2048), IDESC_MN, (unsigned) (i | ks));
-                        umma(dcol, da, smem_desc(plo + ks * 256, 128, 2048), IDESC_MN, 1u);
+                        for (int ks = 0; ks < 8; ks++)
+                            umma(dcol, a_lo + (ks * 4096 >> 4), hi_k, b_lo + (ks * (2 * AR / 8 * 128) >> 4), hi_k, IDESC_K, (unsigned) (h | ks));
+                        umma_commit(&sm.op_empty[os]);
                     }
-                    umma_commit(&sm.op_empty[os]);
+                    umma_commit(&sm.s_full[sb]);
+                    nk++;
+                } else { // O^T += V^T P^T(nv), P as its high and low parts
+                    TC_STAMP(nv, 16);
+                    tc_wait(&sm.p_full, nv & 1, &sm.dead, a.status);
+                    TC_STAMP(nv, 17);
+#pragma unroll 1
+                    for (int h = 0; h < 2; h++, oseq++) {
+                        const int os = oseq % NOP;
+                        tc_wait(&sm.op_full[os], (oseq / NOP) & 1, &sm.dead, a.status);
+                        if (h == 0) TC_STAMP(nv, 18);
+                        tc_fence_after();
+                        const unsigned a_lo = desc_lo(smem_u32(sm.op[os]), 128), dcol = tb + (h ? O_COL1 : O_COL0);
+#pragma unroll
+                        for (int ks = 0; ks < 8; ks++) // B: the 48 rows of P's high part, then the 48 of its low part (12 row groups)
+                            umma(dcol, a_lo + (ks * 256 >> 4), hi_mn, p_lo0 + (ks * 256 >> 4), hi_mn, IDESC_MN, (unsigned) (nv | ks));
+                        umma_commit(&sm.op_empty[os]);
+                    }
+                    umma_commit(&sm.p_empty);
+                    TC_STAMP(nv, 19);
+                    nv++;
                 }
-                umma_commit(&sm.p_empty);
-                TC_STAMP(i, 19);
-            };
-            if (G > 0) do_S(0);
-            if (G > 1) do_S(1);
-            for (int i = 0; i < G; i++) {
-                do_PV(i);
-                if (i + 2 < G) do_S(i + 2);
             }
         }
-    } else {
-        // ---- workers: warp = 4 c + q: tile q (positions 32 q .. + 31 of a group, tensor-memory lanes 32 q ..), query rows
-        // 12 c .. 12 c + 11 in the softmax, dims 32 (4 h + c) .. + 31 of half h in the unpacking ----
-        const int q = warp & 3, c = warp >> 2, prow = ATP * q + lane;
-        const unsigned pos_off = (prow >> 3) * 128 + (prow & 7) * 16; // the position's 16-byte unit inside a dim / row group
-        const unsigned lane_addr = tb + ((unsigned) (ATP * q) << 16);
-        const bool owner = q == 0 && lane < RS; // owns query row r_own: its running / reference max, the exchange
-        const int r_own = RS * c + (lane < RS ? lane : 0);
+    } else if (warp >= NSOFT && warp < W_ISSUE) {
+        // ---- unpack warps: packed rows -> operand slots, both 128-dim halves of one side of a group at a time ----
+        const int w = warp - NSOFT, q = w & 3, c = w >> 2, prow = ATP * q + lane;
+        const unsigned pos_off = (prow >> 3) * 128 + (prow & 7) * 16; // the position's 16-byte unit inside a dim group
+        const bool st = w == 0;
         unsigned rseq = 0, oseq = 0;
-        float l_acc[RS], s[RS];
-#pragma unroll
-        for (int i = 0; i < RS; i++) l_acc[i] = 0.f, s[i] = 0.f;
-        float m_acc = -CUDART_INF_F;
-        unsigned long long w0 = 0, w1 = 0, w2 = 0;
-
-        // both 128-dim halves of one side of a group: packed rows -> operand slots
-        auto unpack = [&](int side, const Task & k, int grp) {
+        for (int nk = 0, nv = 0; nv < G;) {
+            const bool isK = nk < G && nk < nv + NSB;
+            const int side = isK ? 0 : 1, grp = isK ? nk - NSB : nv;
+            const Task k = get_task(kk + (isK ? nk : nv) * a.cph);
             const int rs = (rseq + q) % NRAW;
-            mbar_wait(&sm.raw_full[rs], ((rseq + q) / NRAW) & 1, a.status);
-            TC_STAMP(grp, side ? 6 : 11);
+            if (st) TC_STAMP(grp, side ? 8 : 11);
+            tc_wait(&sm.raw_full[rs], ((rseq + q) / NRAW) & 1, &sm.dead, a.status);
+            if (st) TC_STAMP(grp, side ? 9 : 12);
             const int tbq = k.pos0 + q * ATP;
             const bool valid = q < k.nt && lane < k.c1 - tbq;
             const int bits = (kv.s[side].rval && tbq >= ws) ? 8 : kv.s[side].bits;
+            // which 32-dim block of the half this lane unpacks: the four warps of a tile cover the four blocks of every row, rotated
+            // with the row so that the 16-byte loads of 8 consecutive lanes (rows 32 bits bytes apart) fall into 8 different
+            // bank groups
+            const int jr = (c + (lane >> (bits == 6 ? 1 : (bits == 5 || bits == 7) ? 2 : 0))) & 3;
+#pragma unroll 1
             for (int h = 0; h < 2; h++, oseq++) {
                 const int os = oseq % NOP;
                 const unsigned round = oseq / NOP;
-                if (round > 0) mbar_wait(&sm.op_empty[os], (round - 1) & 1, a.status);
-                TC_STAMP(grp, (side ? 7 : 12) + 2 * h);
-                dq_item_any(bits, sm.raw[rs], lane, 4 * h + c, valid, sm.op[os] + 4 * c * 2048 + pos_off);
+                if (round > 0) tc_wait(&sm.op_empty[os], (round - 1) & 1, &sm.dead, a.status);
+                dq_item_any(bits, sm.raw[rs], lane, 4 * h + jr, valid, sm.op[os] + 4 * jr * 2048 + pos_off);
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.op_full[os]);
-                TC_STAMP(grp, (side ? 8 : 13) + 2 * h);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.raw_empty[rs]);
+            if (st) TC_STAMP(grp, side ? 10 : 13);
             rseq += GT;
-        };
-        auto xbase = [&](const Task & k) -> size_t { return (((size_t) g * ATT_NCH + k.c) * a.nbmax) * AR + r_own; };
-
-        // S^T of group j is complete: scores to registers, mask, tile maxima, the group's own maxima published, the words
-        // the running max will need requested
-        auto scores = [&](int j, const Task & k) {
-            mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1, a.status);
-            TC_STAMP(j - 1, 4);
-            tc_fence_after();
-            tmem_ld12(lane_addr + ((j & 1) ? S_COL1 : S_COL0) + RS * c, s);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.s_empty[j & 1]);
-            const int p_abs = k.pos0 + prow;
-            if (k.pos0 + GP - 1 > min(k.c1 - 1, n) || R < AR) { // (uniform) row token t sees positions <= n + t; chunk end; padding rows
+            if (isK) nk++;
+            else nv++;
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+        // ---- softmax warps: warp = 4 c2 + q: positions 32 q .. + 31 of a group (tensor-memory lanes 32 q ..), query rows
+        // 24 c2 .. + 23. Lanes 0 .. 23 own one row each (its running / reference max; replicated over the four q) ----
+        const int q = warp & 3, c2 = warp >> 2, prow = ATP * q + lane, row0 = RS * c2;
+        const unsigned pos_off = (prow >> 3) * 128 + (prow & 7) * 16;
+        const unsigned lane_addr = tb + ((unsigned) (ATP * q) << 16);
+        const bool owner = lane < RS, st = warp == 0;
+        const int r_own = row0 + (owner ? lane : 0);
+        WarpScratch & W = sm.ws[warp];
+        float l_acc[RS];
 #pragma unroll
+        for (int i = 0; i < RS; i++) l_acc[i] = 0.f;
+        float m_acc = -CUDART_INF_F;
+        unsigned long long w0 = 0, w1 = 0, w2 = 0;
+        auto xbase = [&](const Task & k) -> size_t { return (((size_t) g * ATT_NCH + k.c) * a.nbmax) * AR + r_own; };
+        // which of the warp's rows this thread's position must not see in group k: row token t sees positions <= n + t; positions
+        // past the chunk end and padding rows see nothing (0 for almost every group: uniform test first)
+        auto row_mask = [&](const Task & k) -> unsigned {
+            unsigned m = 0u;
+            if (k.pos0 + GP - 1 > min(k.c1 - 1, n) || R < AR) {
+                const int p_abs = k.pos0 + prow;
+#pragma unroll 1
                 for (int i = 0; i < RS; i++) {
-                    const int r = RS * c + i, lim = min(k.c1 - 1, n + (int) sm.rtok[r]);
-                    if (p_abs > lim || r >= R) s[i] = -CUDART_INF_F;
+                    const int r = row0 + i;
+                    if (p_abs > min(k.c1 - 1, n + (int) sm.rtok[r]) || r >= R) m |= 1u << i;
                 }
             }
-            float mx[RS];
+            return m;
+        };
+        // rows row0 + 8 gq .. + 7 of S^T of group j: request, then (after the wait) as masked floats
+        auto scores_request = [&](int j, int gq, unsigned (&r)[8]) { tmem_ld8_async(lane_addr + S_COL + S_STRIDE * (j % NSB) + row0 + 8 * gq, r); };
+        auto scores_take = [&](unsigned (&r)[8], unsigned mask, int gq, float (&s)[8]) {
+            tmem_wait8(r);
 #pragma unroll
-            for (int i = 0; i < RS; i++) mx[i] = key2f(__reduce_max_sync(FULL_MASK, f2key(s[i])));
-            if (lane == 0) {
-                float4 * d = reinterpret_cast<float4 *>(&sm.tmax[q][RS * c]);
-                d[0] = make_float4(mx[0], mx[1], mx[2], mx[3]);
-                d[1] = make_float4(mx[4], mx[5], mx[6], mx[7]);
-                d[2] = make_float4(mx[8], mx[9], mx[10], mx[11]);
+            for (int i = 0; i < 8; i++) s[i] = __uint_as_float(r[i]);
+            if (__any_sync(FULL_MASK, mask != 0u)) {
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    if ((mask >> (8 * gq + i)) & 1u) s[i] = -CUDART_INF_F;
             }
-            named_bar(1 + c, 4 * 32);
+        };
+        // tile maxima of group j, its own maxima published, the words its running max will need requested
+        auto maxima = [&](int j, const Task & k) {
+            if (st) TC_STAMP(j, 0);
+            tc_wait(&sm.s_full[j % NSB], (j / NSB) & 1, &sm.dead, a.status);
+            if (st) TC_STAMP(j, 1);
+            tc_fence_after();
+            unsigned ra[8], rb[8], rc[8];
+            scores_request(j, 0, ra);
+            scores_request(j, 1, rb);
+            scores_request(j, 2, rc);
+            const unsigned mask = row_mask(k);
+#pragma unroll
+            for (int gq = 0; gq < RS / 8; gq++) {
+                float s[8];
+                scores_take(gq == 0 ? ra : gq == 1 ? rb : rc, mask, gq, s);
+                int kx[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) kx[i] = __reduce_max_sync(FULL_MASK, f2key(s[i]));
+                if (lane == 0) {
+                    int4 * d = reinterpret_cast<int4 *>(&sm.tmax[j % 3][q][row0 + 8 * gq]);
+                    d[0] = make_int4(kx[0], kx[1], kx[2], kx[3]);
+                    d[1] = make_int4(kx[4], kx[5], kx[6], kx[7]);
+                }
+            }
+            named_bar(1 + c2, GT * 32);
+            if (owner && q == 0 && k.nb > 1 && k.b + 1 < k.nb) {
+                const int(&tm)[GT][AR] = sm.tmax[j % 3];
+                const int gk = max(max(tm[0][r_own], tm[1][r_own]), max(tm[2][r_own], tm[3][r_own]));
+                __stcg(a.xa + xbase(k) + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(key2f(gk)));
+            }
+            if (st) TC_STAMP(j, 2);
+        };
+        // the words the running max of group k will need: requested one phase before they are used, when the CTAs that hold
+        // the chunk's previous groups have most likely published them
+        auto request_words = [&](const Task & k) {
             if (owner && k.nb > 1) {
                 const size_t xb0 = xbase(k);
-                if (k.b + 1 < k.nb) {
-                    const float gm = fmaxf(fmaxf(sm.tmax[0][r_own], sm.tmax[1][r_own]), fmaxf(sm.tmax[2][r_own], sm.tmax[3][r_own]));
-                    __stcg(a.xa + xb0 + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(gm));
-                }
                 if (k.b >= 1) w1 = __ldcv(a.xa + xb0 + (size_t) (k.b - 1) * AR);
                 if (k.b >= 2) w2 = __ldcv(a.xa + xb0 + (size_t) (k.b - 2) * AR);
                 if (k.b >= 3) w0 = __ldcv(a.xb + xb0 + (size_t) (k.b - 3) * AR);
             }
-            TC_STAMP(j - 1, 5);
         };
-
-        // P of group i from the scores in registers
+        // P of group i
         auto softmax = [&](int i, const Task & k) {
-            const int par = i & 1;
-            TC_STAMP(i, 0);
+            if (st) TC_STAMP(i, 3);
+            float beta = 0.f, f = 1.f;
             if (owner) {
                 float m_in = -CUDART_INF_F;
                 const size_t xb0 = xbase(k);
@@ -420,131 +582,143 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     if (k.b >= 2) m_in = fmaxf(m_in, poll_word(a.xa + xb0 + (size_t) (k.b - 2) * AR, w2, a.epoch, a.status));
                     if (k.b >= 3) m_in = fmaxf(m_in, poll_word(a.xb + xb0 + (size_t) (k.b - 3) * AR, w0, a.epoch, a.status));
                 }
-                float mr[GT], m = m_in;
+                if (st) TC_STAMP(i, 7);
+                const int(&tm)[GT][AR] = sm.tmax[i % 3];
+                int kr = f2key(m_in), kM;
 #pragma unroll
-                for (int t = 0; t < GT; t++) {
-                    m = fmaxf(m, sm.tmax[t][r_own]);
-                    mr[t] = m;
-                    sm.mrun[par][t][r_own] = m;
-                }
-                if (k.nb > 1 && k.b + 3 < k.nb) __stcg(a.xb + xb0 + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(m));
-                float f = 1.f;
-                if (m != -CUDART_INF_F) {
-                    if (m_acc == -CUDART_INF_F) m_acc = m;
-                    else if (m > m_acc + REF_SLACK) {
-                        f = expf(m_acc - m);
-                        m_acc = m;
+                for (int t = 0; t < GT; t++)
+                    if (t <= q) kr = max(kr, tm[t][r_own]);
+                kM = kr;
+#pragma unroll
+                for (int t = 0; t < GT; t++)
+                    if (t > q) kM = max(kM, tm[t][r_own]);
+                const float mr = key2f(kr), M = key2f(kM);
+                if (q == 0 && k.nb > 1 && k.b + 3 < k.nb) __stcg(a.xb + xb0 + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(M));
+                if (M != -CUDART_INF_F) {
+                    if (m_acc == -CUDART_INF_F) m_acc = M + REF_MARGIN;
+                    else if (M > m_acc + REF_SLACK) {
+                        f = exp_any(m_acc - (M + REF_MARGIN));
+                        m_acc = M + REF_MARGIN;
                     }
                 }
-#pragma unroll
-                for (int t = 0; t < GT; t++) sm.beta[par][t][r_own] = mr[t] == -CUDART_INF_F ? 0.f : expf(mr[t] - m_acc);
-                sm.fsc[par][r_own] = f;
-                if (f != 1.f) atomicOr(&sm.resc[par], 1);
+                beta = mr == -CUDART_INF_F ? 0.f : exp_any(mr - m_acc);
+                W.m[lane] = mr == -CUDART_INF_F ? CUDART_INF_F : mr;
+                W.beta[lane] = beta;
+                W.f[lane] = f;
             }
-            named_bar(5, NWORK * 32);
-            if (tid == 0) sm.resc[par ^ 1] = 0;
-            TC_STAMP(i, 1);
-            if (i > 0) mbar_wait(&sm.p_empty, (i - 1) & 1, a.status); // P V of the previous group is complete: P is free, O^T at rest
-            TC_STAMP(i, 2);
+            if (st) TC_STAMP(i, 14);
+            const float bnext = __shfl_down_sync(FULL_MASK, beta, 1);
+            if (owner && !(lane & 1)) {
+                const __half2 bh = __floats2half2_rn(beta, bnext);
+                const float2 bf = __half22float2(bh);
+                const __half2 bl = __floats2half2_rn(beta - bf.x, bnext - bf.y);
+                W.bh[lane >> 1] = *reinterpret_cast<const unsigned *>(&bh);
+                W.bl[lane >> 1] = *reinterpret_cast<const unsigned *>(&bl);
+            }
+            const unsigned anyf = __ballot_sync(FULL_MASK, owner && f != 1.f);
+            __syncwarp();
+            if (st) TC_STAMP(i, 4);
+            if (i > 0) tc_wait(&sm.p_empty, (i - 1) & 1, &sm.dead, a.status); // P V of the previous group is complete: P is free, O^T at rest
+            if (st) TC_STAMP(i, 5);
             tc_fence_after();
-            if (sm.resc[par]) { // a reference max moved: bring the accumulator rows (and the row sums) to it
-                float fs[RS], v[RS];
+            if (anyf && a.prof && st && lane == 0) a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 15] += 1ull | ((unsigned long long) __popc(anyf) << 32);
+            if (anyf) { // a reference max moved: bring this warp's block of the accumulator (and its row sums) to it
+#pragma unroll 1
+                for (int hg = 0; hg < 4 * (RS / 8); hg++) { // (half, high / low block, 8 columns)
+                    const int h = hg / (2 * (RS / 8)), pt = (hg / (RS / 8)) & 1, gq = hg % (RS / 8);
+                    if (!((anyf >> (8 * gq)) & 0xffu)) continue; // no row of these 8 moved
+                    const unsigned ad = lane_addr + (h ? O_COL1 : O_COL0) + AR * pt + row0 + 8 * gq;
+                    float v[8];
+                    tmem_ld8(ad, v);
 #pragma unroll
-                for (int j = 0; j < RS; j++) fs[j] = sm.fsc[par][RS * c + j];
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const unsigned ad = lane_addr + (h ? O_COL1 : O_COL0) + RS * c;
-                    tmem_ld12(ad, v);
-#pragma unroll
-                    for (int j = 0; j < RS; j++) v[j] *= fs[j];
-                    tmem_st12(ad, v);
+                    for (int j = 0; j < 8; j++) v[j] *= W.f[8 * gq + j];
+                    tmem_st8(ad, v);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < RS; j++) l_acc[j] *= fs[j];
+                for (int j = 0; j < RS; j++) l_acc[j] *= W.f[j];
             }
-            float mq[RS], bq[RS];
-            {
-                const float4 * mp = reinterpret_cast<const float4 *>(&sm.mrun[par][q][RS * c]);
-                const float4 * bp = reinterpret_cast<const float4 *>(&sm.beta[par][q][RS * c]);
+            const unsigned mask = row_mask(k);
+            unsigned ra[8], rb[8];
+            scores_request(i, 0, ra);
 #pragma unroll
-                for (int j = 0; j < 3; j++) {
-                    const float4 mv = mp[j], bv = bp[j];
-                    mq[4 * j] = mv.x, mq[4 * j + 1] = mv.y, mq[4 * j + 2] = mv.z, mq[4 * j + 3] = mv.w;
-                    bq[4 * j] = bv.x, bq[4 * j + 1] = bv.y, bq[4 * j + 2] = bv.z, bq[4 * j + 3] = bv.w;
-                }
-            }
-            unsigned hi2[RS / 2], lo2[RS / 2];
-#pragma unroll
-            for (int j = 0; j < RS / 2; j++) {
-                float p0 = 0.f, p1 = 0.f;
-                if (mq[2 * j] != -CUDART_INF_F) p0 = expf(s[2 * j] - mq[2 * j]);
-                if (mq[2 * j + 1] != -CUDART_INF_F) p1 = expf(s[2 * j + 1] - mq[2 * j + 1]);
-                l_acc[2 * j] = __fmaf_rn(bq[2 * j], p0, l_acc[2 * j]);
-                l_acc[2 * j + 1] = __fmaf_rn(bq[2 * j + 1], p1, l_acc[2 * j + 1]);
-                const float2 pf = __half22float2(__floats2half2_rn(p0, p1)); // the reference's fp16 P
-                const float x0 = __fmul_rn(pf.x, bq[2 * j]), x1 = __fmul_rn(pf.y, bq[2 * j + 1]);
-                const __half2 hh = __floats2half2_rn(x0, x1);
-                const float2 hf = __half22float2(hh);
-                const __half2 ll = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
-                hi2[j] = *reinterpret_cast<const unsigned *>(&hh);
-                lo2[j] = *reinterpret_cast<const unsigned *>(&ll);
-            }
-            // rows 12 c .. 12 c + 11 of position prow: row group (12 c) >> 3 from its row (12 c) & 7 (0 or 4) on, then the next
-            {
-                const int ng0 = (RS * c) >> 3;
-                uint8_t * ph = sm.p[0] + ng0 * 2048 + pos_off;
-                uint8_t * pl = sm.p[1] + ng0 * 2048 + pos_off;
-                if (c & 1) {
-                    *reinterpret_cast<uint2 *>(ph + 8) = make_uint2(hi2[0], hi2[1]);
-                    *reinterpret_cast<uint4 *>(ph + 2048) = make_uint4(hi2[2], hi2[3], hi2[4], hi2[5]);
-                    *reinterpret_cast<uint2 *>(pl + 8) = make_uint2(lo2[0], lo2[1]);
-                    *reinterpret_cast<uint4 *>(pl + 2048) = make_uint4(lo2[2], lo2[3], lo2[4], lo2[5]);
+            for (int gq = 0; gq < RS / 8; gq++) { // three row groups of 8: one 16-byte unit of each P part; the next group's
+                                                  // scores are in flight while this one's P is computed
+                float s[8];
+                if (gq + 1 < RS / 8) {
+                    if (gq & 1) {
+                        scores_take(rb, mask, gq, s);
+                        scores_request(i, gq + 1, ra);
+                    } else {
+                        scores_take(ra, mask, gq, s);
+                        scores_request(i, gq + 1, rb);
+                    }
                 } else {
-                    *reinterpret_cast<uint4 *>(ph) = make_uint4(hi2[0], hi2[1], hi2[2], hi2[3]);
-                    *reinterpret_cast<uint2 *>(ph + 2048) = make_uint2(hi2[4], hi2[5]);
-                    *reinterpret_cast<uint4 *>(pl) = make_uint4(lo2[0], lo2[1], lo2[2], lo2[3]);
-                    *reinterpret_cast<uint2 *>(pl + 2048) = make_uint2(lo2[4], lo2[5]);
+                    scores_take((gq & 1) ? rb : ra, mask, gq, s);
                 }
+                if (gq == RS / 8 - 1) { // the last read of this S^T buffer
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm.s_empty[i % NSB]);
+                }
+                const float4 ma = *reinterpret_cast<const float4 *>(&W.m[8 * gq]), mb = *reinterpret_cast<const float4 *>(&W.m[8 * gq + 4]);
+                const float4 ba = *reinterpret_cast<const float4 *>(&W.beta[8 * gq]), bb = *reinterpret_cast<const float4 *>(&W.beta[8 * gq + 4]);
+                const uint4 bhv = *reinterpret_cast<const uint4 *>(&W.bh[4 * gq]), blv = *reinterpret_cast<const uint4 *>(&W.bl[4 * gq]);
+                const float mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w}, be[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
+                const unsigned bhw[4] = {bhv.x, bhv.y, bhv.z, bhv.w}, blw[4] = {blv.x, blv.y, blv.z, blv.w};
+                unsigned hi[4], lo[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int r = 8 * gq + 2 * j;
+                    const float p0 = exp_neg(s[2 * j] - mm[2 * j]), p1 = exp_neg(s[2 * j + 1] - mm[2 * j + 1]);
+                    l_acc[r] = __fmaf_rn(be[2 * j], p0, l_acc[r]);
+                    l_acc[r + 1] = __fmaf_rn(be[2 * j + 1], p1, l_acc[r + 1]);
+                    const __half2 ph = __floats2half2_rn(p0, p1); // the reference's fp16 P
+                    const __half2 bh = *reinterpret_cast<const __half2 *>(&bhw[j]), bl = *reinterpret_cast<const __half2 *>(&blw[j]);
+                    const __half2 hh = __hmul2(ph, bh);                 // P beta = hh + ll up to 2^-22: the product's exact residual
+                    const __half2 ll = __hfma2(ph, bl, __hfma2(ph, bh, __hneg2(hh))); // plus the low part of beta
+                    hi[j] = *reinterpret_cast<const unsigned *>(&hh);
+                    lo[j] = *reinterpret_cast<const unsigned *>(&ll);
+                }
+                const unsigned off = (unsigned) ((RS / 8) * c2 + gq) * 2048 + pos_off;
+                *reinterpret_cast<uint4 *>(sm.p[0] + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4 *>(sm.p[1] + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
             fence_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_full);
-            TC_STAMP(i, 3);
+            if (st) TC_STAMP(i, 6);
         };
 
         if (G > 0) {
-            Task kc = get_task(kk), kn = kc, k2 = kc;
-            unpack(0, kc, 99);
-            if (G > 1) {
-                kn = get_task(kk + a.cph);
-                unpack(0, kn, 99);
-            }
-            scores(0, kc);
-            for (int i = 0; i < G; i++) {
-                softmax(i, kc);
-                if (i + 1 < G) scores(i + 1, kn);
-                unpack(1, kc, i);
-                if (i + 2 < G) {
-                    k2 = get_task(kk + (i + 2) * a.cph);
-                    unpack(0, k2, i);
+            Task kc = get_task(kk), kn = kc;
+            for (int i = -1; i < G; i++) { // maxima of group i + 1, then P of group i
+                if (i + 1 < G) {
+                    kn = get_task(kk + (i + 1) * a.cph);
+                    maxima(i + 1, kn);
                 }
+                if (i >= 0) softmax(i, kc);
+                if (i + 1 < G) request_words(kn);
                 kc = kn;
-                kn = k2;
             }
-            mbar_wait(&sm.p_empty, (G - 1) & 1, a.status);
+            tc_wait(&sm.p_empty, (G - 1) & 1, &sm.dead, a.status);
             tc_fence_after();
         }
         // ---- the CTA's partial: O^T lanes are dims, columns are query rows ----
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v[RS];
-            if (G > 0) tmem_ld12(lane_addr + (h ? O_COL1 : O_COL0) + RS * c, v);
+#pragma unroll 1
+        for (int hg = 0; hg < 2 * (RS / 8); hg++) {
+            const int h = hg / (RS / 8), gq = hg % (RS / 8);
+            float v[8], w[8];
+            if (G > 0) {
+                tmem_ld8(lane_addr + (h ? O_COL1 : O_COL0) + row0 + 8 * gq, v);
+                tmem_ld8(lane_addr + (h ? O_COL1 : O_COL0) + AR + row0 + 8 * gq, w);
+            }
 #pragma unroll
-            for (int j = 0; j < RS; j++) {
-                const int r = RS * c + j;
-                if (r < R) a.part[((size_t) slot * AR + r) * HD + 128 * h + prow] = G > 0 ? v[j] : 0.f;
+            for (int j = 0; j < 8; j++) {
+                const int r = row0 + 8 * gq + j;
+                if (r < R) a.part[((size_t) slot * AR + r) * HD + 128 * h + prow] = G > 0 ? v[j] + w[j] : 0.f;
             }
         }
 #pragma unroll
@@ -552,15 +726,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             float x = l_acc[j];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(FULL_MASK, x, o);
-            if (lane == 0) sm.lsum[q][RS * c + j] = x;
+            l_acc[j] = x;
         }
-        named_bar(5, NWORK * 32);
-        if (owner && r_own < R)
-            a.ml[(size_t) slot * AR + r_own] = make_float2(m_acc, sm.lsum[0][r_own] + sm.lsum[1][r_own] + sm.lsum[2][r_own] + sm.lsum[3][r_own]);
+        named_bar(5, NSOFT * 32); // every softmax warp is past its last read of the tile maxima
+        float(&lsum)[GT][AR] = *reinterpret_cast<float(*)[GT][AR]>(&sm.tmax[0][0][0]);
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < RS; j++) lsum[q][row0 + j] = l_acc[j];
+        }
+        named_bar(5, NSOFT * 32);
+        if (owner && q == 0 && r_own < R)
+            a.ml[(size_t) slot * AR + r_own] = make_float2(m_acc, lsum[0][r_own] + lsum[1][r_own] + lsum[2][r_own] + lsum[3][r_own]);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == NWORK) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(TMEM_COLS) : "memory");
+    if (warp == W_ISSUE) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(TMEM_COLS) : "memory");
 }
 
 } // namespace tc

@@ -142,7 +142,8 @@ def test_slots_batch_matches_single(mk, torch_cuda):
         O1 = torch.zeros((T, 24, 256), dtype=torch.float32, device="cuda")
         eng.attend(0, L, torch.from_numpy(Qs[s]).cuda(), O1, seq=s)
         eng.sync()
-        assert np.abs(O1.cpu().numpy() - O[r:r + T]).max() <= 5e-4  # two kernels (batched / single): fp32 summation order, a rare fp16 flip of P
+        # two kernels (batched / single), same arithmetic: fp32 summation order, now and then an fp16 rounding of P the other way
+        check_edge(O1.cpu().numpy(), O[r:r + T], np.maximum(kvdata.channel_scales(60 + s, 0, 1), kvdata.channel_scales(80 + s, 0, 1)), ("single", s))
         for p in (L, L + T - 1):
             a, sa = eng.read_row(0, 0, 3, p, seq=s)
             b, sb = orcs[s].row(0, 0, 3, p)

@@ -34,7 +34,10 @@ def test_attend_static_matches_attend_twice(mk, torch_cuda):
     assert torch.cuda.mem_get_info()[0] >= free_before  # nothing was taken from the device allocator by the two calls
     for layer, n, Q, ref, out in cases:
         assert torch.isfinite(out).all()
-        assert float((out - ref).abs().max()) <= 2e-3
+        # the two entry points may run different kernels (same arithmetic; an fp16 rounding of P can fall the other way):
+        # the bound of the short-context attention tests
+        from test_gpu_attend import check_edge
+        check_edge(out.cpu().numpy(), ref.cpu().numpy(), kvdata.channel_scales(40 + layer, layer, 1), ("static", layer))
     Q9 = torch.zeros((9, 24, 256), dtype=torch.float16, device="cuda")
     O9 = torch.zeros((9, 24, 256), dtype=torch.float32, device="cuda")
     with pytest.raises(mk.EngineError, match="fixed scratch"):
