@@ -29,9 +29,9 @@ for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
 LAYERS, CTX0, T_STEP, WIN = 16, 101600, 8, 2048
 SPEC = "K*=5r,V*=6"
 NH, NKV, HD = 24, 4, 256
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fast_kernel launch at this workload's shapes (ncu capture of the
-# one-layer case, profiles/attn_fast_kernel_config2_one_layer.md; a launch of the 16-layer run processes the same one layer)
-NCU_TRAFFIC_BYTES = 166.2e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch at this workload's shapes (ncu capture of the
+# one-layer case, profiles/attn_tc_kernel_config2_one_layer.md; a launch of the 16-layer run processes the same one layer)
+NCU_TRAFFIC_BYTES = 165.8e6
 WORKLOAD = "config2: 16 attention layers, 101,600 positions, preset F layout K5r/V6 + q8_0 window 2048, 8 queries/step, streaming append+spill+attend"
 
 
@@ -313,41 +313,55 @@ def main():
     # per-step inputs, device resident (value) and pinned host (e2e)
     rng = np.random.default_rng(2)
     accepted = rng.integers(1, T_STEP + 1, size=total_steps)
-    Kd = [None] * layers; Vd = [None] * layers
+    Kl = [None] * layers; Vl = [None] * layers
     for l in range(layers):
-        Kd[l], Vd[l] = rows(l, T_STEP)
+        Kl[l], Vl[l] = rows(l, T_STEP)
+    Kd = torch.stack(Kl); Vd = torch.stack(Vl)  # [layers][T][4][256]
     Qd = torch.randn((layers, T_STEP, NH, HD), generator=g, device="cuda").half()
     Od = torch.empty((layers, T_STEP, NH, HD), dtype=torch.float32, device="cuda")
-    Kh = torch.stack(Kd).cpu().pin_memory(); Vh = torch.stack(Vd).cpu().pin_memory(); Qh = Qd.cpu().pin_memory()
+    Kh = Kd.cpu().pin_memory(); Vh = Vd.cpu().pin_memory(); Qh = Qd.cpu().pin_memory()
     Oh = torch.empty((layers, T_STEP, NH, HD), dtype=torch.float32).pin_memory()
-    Ks = torch.empty_like(torch.stack(Kd)); Vs = torch.empty_like(Ks); Qs = torch.empty_like(Qd)
+    Ks = torch.empty_like(Kd); Vs = torch.empty_like(Vd); Qs = torch.empty_like(Qd)
 
     state = {"n": ctx0, "i": 0, "bytes": 0}
-    def one_step(host=False, time_attend=None):
-        n = state["n"]
-        T = mk.cap_T(n, T_STEP)
-        for l in range(layers):
-            if host:  # end to end: this step's rows come from pinned host memory, the result goes back
-                Ks[l].copy_(Kh[l], non_blocking=True); Vs[l].copy_(Vh[l], non_blocking=True); Qs[l].copy_(Qh[l], non_blocking=True)
-                k, v, q = Ks[l], Vs[l], Qs[l]
-            else:
-                k, v, q = Kd[l], Vd[l], Qd[l]
-            eng.append_raw(l, n, T, k, v)
-            if time_attend is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-            eng.attend(l, n, q[:T], Od[l, :T])
-            if time_attend is not None:
-                e1.record(stream)
-                time_attend.append((e0, e1))
-            if host:
-                Oh[l].copy_(Od[l], non_blocking=True)
-            state["bytes"] += algorithmic_bytes(n, T)
-        if host:
-            stream.synchronize()  # the caller reads the step's result
+
+    def advance(n, T):
+        state["bytes"] += layers * algorithmic_bytes(n, T)
         state["n"] = n + min(T, int(accepted[state["i"]]))
         state["i"] += 1
         eng.commit(state["n"])
+
+    def one_step(host=False):
+        """one decode step: every layer appends T rows and attends (one library call for the whole step)"""
+        n = state["n"]
+        T = mk.cap_T(n, T_STEP)
+        if host:  # end to end: this step's rows come from pinned host memory, the result goes back
+            Ks.copy_(Kh, non_blocking=True); Vs.copy_(Vh, non_blocking=True); Qs.copy_(Qh, non_blocking=True)
+            eng.step_layers(n, Ks[:, :T], Vs[:, :T], Qs[:, :T], Od[:, :T])
+            Oh.copy_(Od, non_blocking=True)
+            stream.synchronize()  # the caller reads the step's result
+        else:
+            eng.step_layers(n, Kd[:, :T], Vd[:, :T], Qd[:, :T], Od[:, :T])
+        advance(n, T)
+
+    filler = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")
+
+    def timed_attends(pairs):
+        """a step whose attention launches carry an event pair each; a few ms of device work is queued first so that the host is
+        ahead of the device and the pairs time device work only"""
+        n = state["n"]
+        T = mk.cap_T(n, T_STEP)
+        for l in range(layers):
+            eng.append_raw(l, n, T, Kd[l], Vd[l])
+        for _ in range(6):
+            filler.fill_(1)
+        for l in range(layers):
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            eng.attend(l, n, Qd[l, :T], Od[l, :T])
+            e1.record(stream)
+            pairs.append((e0, e1))
+        advance(n, T)
 
     def barrier():
         torch.cuda.synchronize()
@@ -376,7 +390,7 @@ def main():
     pairs = []
     state["bytes"] = 0
     for _ in range(min(args.steps, 8)):
-        one_step(time_attend=pairs)
+        timed_attends(pairs)
     torch.cuda.synchronize()
     att_ms = [a.elapsed_time(b) for a, b in pairs]
     att_bytes = state["bytes"] / len(pairs)
@@ -418,7 +432,7 @@ def main():
             "per_gpu_us_per_layer": us_layer,
             "hbm_gbs_step": step_bytes / (ms * 1e-3) / 1e9 * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES if (layers == LAYERS and ctx0 == CTX0) else None,
-                         "kernel": "attn_fast_kernel (+ merge)", "us_per_launch": att_us, "bytes_per_launch": att_bytes, "peak_source": peak_src},
+                         "kernel": "attn_tc_kernel (+ merge)", "us_per_launch": att_us, "bytes_per_launch": att_bytes, "peak_source": peak_src},
             "e2e": {"value": 1e3 * ms_e2e / units, "unit": "us/layer",
                     "h2d_bytes_per_step": int(layers * (2 * T_STEP * NKV * HD * 2 + T_STEP * NH * HD * 2)),
                     "d2h_bytes_per_step": int(layers * T_STEP * NH * HD * 4)},

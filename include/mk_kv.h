@@ -82,6 +82,11 @@ int mk_kv_attend_partial(void * h, int seq, int layer, int n, int T, const void 
 int mk_kv_combine(void * h, int layer, int T, int nparts, const void * parts, const void * mls, void * O);
 /* append + attend of one decode step's layer, as the reference's attention phase does in one pass */
 int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O);
+/* One decode step over layers 0 .. nlayers - 1 in one call: layer l appends T rows at n from K + l kv_stride, V + l kv_stride
+ * and attends with Q + l q_stride into O + l o_stride (strides in bytes). What the reference's forward pass does between its
+ * layers' attention phases (engine.cu:1353-1413) with the host out of the loop; equal to nlayers calls of mk_kv_step. */
+int mk_kv_step_layers(void * h, int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O,
+                      size_t kv_stride, size_t q_stride, size_t o_stride);
 /* lanes_step (lanes.cu:452-560): one pass over several sequences; job j runs T[j] tokens at n[j] of sequence seqs[j].
  * K, V [sum T][4][256], Q [sum T][24][256], O [sum T][24][256] packed in job order. seqs, n, T are host arrays.
  * mk_kv_reserve_batch(njobs) must have been called once with at least this many jobs. */

@@ -71,6 +71,7 @@ struct Smem {
     unsigned char rtok[AR];     // token of a query row
     unsigned tmem_base;
     int dead;                   // a wait of this CTA gave up: no later wait blocks
+    AttnTask tasks[8];          // the CTA's groups as the producer reaches them, by group % 8 (no role is 8 groups apart from it)
     uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[NSB], s_empty[NSB], p_full, p_empty;
     AttnJob job;
 };
@@ -88,11 +89,20 @@ struct Args {
     unsigned long long * prof; // optional: [CTA][16 groups][20] globaltimer stamps: softmax warp 0 (0 .. 7), unpack warp 8 (8 .. 15),
                                // issuer (16 .. 19)
 };
+#ifndef MKKV_TC_PROF
+#define MKKV_TC_PROF 0 // 1: compile the phase stamps in (they cost a few per cent)
+#endif
+#if MKKV_TC_PROF
 #define TC_STAMP(grp, k)                                                                                               \
     do {                                                                                                               \
         if (a.prof && lane == 0 && (grp) >= 0 && (grp) < 16)                                                           \
             a.prof[((size_t) blockIdx.x * 16 + (grp)) * 20 + (k)] = globaltimer_ns();                                  \
     } while (0)
+#else
+#define TC_STAMP(grp, k)                                                                                               \
+    do {                                                                                                               \
+    } while (0)
+#endif
 
 // Wait for a phase of an mbarrier. A failed try suspends the thread in hardware for up to the hinted time (it wakes when the phase
 // completes), so waiting warps take next to no issue slots. Bounded: after WAIT_ROUNDS failed tries the status word and the CTA's
@@ -387,7 +397,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             unsigned rseq = 0;
             for (int nk = 0, nv = 0; nv < G;) { // K runs NSB groups ahead of V
                 const bool isK = nk < G && nk < nv + NSB;
-                const Task k = get_task(kk + (isK ? nk : nv) * a.cph);
+                Task k;
+                if (isK) { // a group's K comes first: its task is computed here, once, and left for the other roles (the waits on
+                           // the copies' barriers order their reads after this write)
+                    k = get_task(kk + nk * a.cph);
+                    sm.tasks[nk & 7] = k;
+                } else {
+                    k = sm.tasks[nv & 7];
+                }
                 const SideSrc & S = isK ? ksrc : vsrc;
                 for (int qq = 0; qq < GT; qq++, rseq++) {
                     const int rs = rseq % NRAW;
@@ -452,36 +469,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         const int w = warp - NSOFT, q = w & 3, c = w >> 2, prow = ATP * q + lane;
         const unsigned pos_off = (prow >> 3) * 128 + (prow & 7) * 16; // the position's 16-byte unit inside a dim group
         const bool st = w == 0;
-        unsigned rseq = 0, oseq = 0;
+        int rs = q, rph = 0, os = 0, oph = 0; // raw slot / phase of this warp's tile, operand slot / phase
+        bool owrap = false;
         for (int nk = 0, nv = 0; nv < G;) {
             const bool isK = nk < G && nk < nv + NSB;
             const int side = isK ? 0 : 1, grp = isK ? nk - NSB : nv;
-            const Task k = get_task(kk + (isK ? nk : nv) * a.cph);
-            const int rs = (rseq + q) % NRAW;
             if (st) TC_STAMP(grp, side ? 8 : 11);
-            tc_wait(&sm.raw_full[rs], ((rseq + q) / NRAW) & 1, &sm.dead, a.status);
+            tc_wait(&sm.raw_full[rs], rph, &sm.dead, a.status);
             if (st) TC_STAMP(grp, side ? 9 : 12);
-            const int tbq = k.pos0 + q * ATP;
-            const bool valid = q < k.nt && lane < k.c1 - tbq;
+            const AttnTask & kr = sm.tasks[(isK ? nk : nv) & 7];
+            const int k_pos0 = kr.pos0;
+            const int2 kt = *reinterpret_cast<const int2 *>(&kr.c1); // c1, nt
+            const int tbq = k_pos0 + q * ATP;
+            const bool valid = q < kt.y && lane < kt.x - tbq;
             const int bits = (kv.s[side].rval && tbq >= ws) ? 8 : kv.s[side].bits;
             // which 32-dim block of the half this lane unpacks: the four warps of a tile cover the four blocks of every row, rotated
             // with the row so that the 16-byte loads of 8 consecutive lanes (rows 32 bits bytes apart) fall into 8 different
             // bank groups
             const int jr = (c + (lane >> (bits == 6 ? 1 : (bits == 5 || bits == 7) ? 2 : 0))) & 3;
 #pragma unroll 1
-            for (int h = 0; h < 2; h++, oseq++) {
-                const int os = oseq % NOP;
-                const unsigned round = oseq / NOP;
-                if (round > 0) tc_wait(&sm.op_empty[os], (round - 1) & 1, &sm.dead, a.status);
+            for (int h = 0; h < 2; h++) {
+                if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.dead, a.status);
                 dq_item_any(bits, sm.raw[rs], lane, 4 * h + jr, valid, sm.op[os] + 4 * jr * 2048 + pos_off);
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.op_full[os]);
+                if (++os == NOP) os = 0, oph ^= 1, owrap = true;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.raw_empty[rs]);
             if (st) TC_STAMP(grp, side ? 10 : 13);
-            rseq += GT;
+            rs += GT;
+            if (rs >= NRAW) rs -= NRAW, rph ^= 1;
             if (isK) nk++;
             else nv++;
         }
@@ -529,9 +548,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             }
         };
         // tile maxima of group j, its own maxima published, the words its running max will need requested
-        auto maxima = [&](int j, const Task & k) {
+        auto maxima = [&](int j) {
             if (st) TC_STAMP(j, 0);
             tc_wait(&sm.s_full[j % NSB], (j / NSB) & 1, &sm.dead, a.status);
+            const Task k = sm.tasks[j & 7];
             if (st) TC_STAMP(j, 1);
             tc_fence_after();
             unsigned ra[8], rb[8], rc[8];
@@ -621,7 +641,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             if (i > 0) tc_wait(&sm.p_empty, (i - 1) & 1, &sm.dead, a.status); // P V of the previous group is complete: P is free, O^T at rest
             if (st) TC_STAMP(i, 5);
             tc_fence_after();
+#if MKKV_TC_PROF
             if (anyf && a.prof && st && lane == 0) a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 15] += 1ull | ((unsigned long long) __popc(anyf) << 32);
+#endif
             if (anyf) { // a reference max moved: bring this warp's block of the accumulator (and its row sums) to it
 #pragma unroll 1
                 for (int hg = 0; hg < 4 * (RS / 8); hg++) { // (half, high / low block, 8 columns)
@@ -692,15 +714,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         };
 
         if (G > 0) {
-            Task kc = get_task(kk), kn = kc;
-            for (int i = -1; i < G; i++) { // maxima of group i + 1, then P of group i
-                if (i + 1 < G) {
-                    kn = get_task(kk + (i + 1) * a.cph);
-                    maxima(i + 1, kn);
+            for (int i = -1; i < G; i++) { // maxima of group i + 1, then P of group i (tasks: left by the producer, see there)
+                if (i + 1 < G) maxima(i + 1);
+                if (i >= 0) {
+                    const Task kc = sm.tasks[i & 7];
+                    softmax(i, kc);
                 }
-                if (i >= 0) softmax(i, kc);
-                if (i + 1 < G) request_words(kn);
-                kc = kn;
+                if (i + 1 < G) {
+                    const Task kn = sm.tasks[(i + 1) & 7];
+                    request_words(kn);
+                }
             }
             tc_wait(&sm.p_empty, (G - 1) & 1, &sm.dead, a.status);
             tc_fence_after();

@@ -51,6 +51,7 @@ def load_library():
         "mk_kv_attend_partial": (i, [vp, i, i, i, i, vp, i, i, vp, vp]),
         "mk_kv_combine": (i, [vp, i, i, i, vp, vp, vp]),
         "mk_kv_step": (i, [vp, i, i, i, i, vp, vp, vp, vp]),
+        "mk_kv_step_layers": (i, [vp, i, i, i, i, vp, vp, vp, vp, C.c_size_t, C.c_size_t, C.c_size_t]),
         "mk_kv_reserve_batch": (i, [vp, i]),
         "mk_kv_step_batch": (i, [vp, i, ip, i, ip, ip, vp, vp, vp, vp]),
         "mk_kv_attend_batch": (i, [vp, i, ip, i, ip, ip, vp, vp]),
@@ -203,6 +204,11 @@ class Engine:
 
     def step(self, layer, n, K, V, Q, O, seq=SEQ_MAIN):
         self._ck(self.L.mk_kv_step(self.h, seq, layer, n, Q.shape[0], _ptr(K), _ptr(V), _ptr(Q), _ptr(O)), "step")
+
+    def step_layers(self, n, K, V, Q, O, seq=SEQ_MAIN):
+        """one decode step over every layer in one call: K, V [layers][T][4][256], Q [layers][T][24][256], O likewise (fp32)"""
+        self._ck(self.L.mk_kv_step_layers(self.h, seq, K.shape[0], n, Q.shape[1], _ptr(K), _ptr(V), _ptr(Q), _ptr(O), K.stride(0) * K.element_size(),
+                                          Q.stride(0) * Q.element_size(), O.stride(0) * O.element_size()), "step_layers")
 
     def reserve_batch(self, njobs):
         self._ck(self.L.mk_kv_reserve_batch(self.h, njobs), "reserve_batch")

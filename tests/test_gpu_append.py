@@ -148,3 +148,31 @@ def test_append_matches_reference_golden_vectors(mk, torch_cuda, bits, rot):
         a, sa = eng.read_row(0, 0, 3, i)
         assert np.array_equal(a, q[i]) and np.array_equal(sa, sc[i]), (bits, rot, i)
     eng.close()
+
+
+def test_step_layers_equals_per_layer_steps(mk, torch_cuda):
+    """mk_kv_step_layers is nlayers calls of mk_kv_step: same row bytes, same outputs"""
+    torch = torch_cuda
+    spec, win, L, T, NL = "K*=5r,V*=6", 2048, 2500, 5, 3
+    a = mk.Engine(NL, L + 64, spec, win)
+    b = mk.Engine(NL, L + 64, spec, win)
+    for l in range(NL):
+        K, V = kvdata.kv_rows(7 + l, l, 0, L)
+        for e in (a, b):
+            e.append(l, 0, torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
+    Ks = torch.stack([torch.from_numpy(kvdata.kv_rows(30 + l, l, L, T)[0]) for l in range(NL)]).cuda()
+    Vs = torch.stack([torch.from_numpy(kvdata.kv_rows(30 + l, l, L, T)[1]) for l in range(NL)]).cuda()
+    Qs = torch.stack([torch.from_numpy(kvdata.q_rows(31, l, L, T)) for l in range(NL)]).cuda()
+    Oa = torch.zeros((NL, T, 24, 256), dtype=torch.float32, device="cuda")
+    Ob = torch.zeros_like(Oa)
+    a.step_layers(L, Ks, Vs, Qs, Oa)
+    for l in range(NL):
+        b.step(l, L, Ks[l], Vs[l], Qs[l], Ob[l])
+    a.sync(); b.sync()
+    assert torch.equal(Oa, Ob)
+    for l in range(NL):
+        for side in (0, 1):
+            ra, sa = a.read_row(l, side, 2, L + T - 1)
+            rb, sb = b.read_row(l, side, 2, L + T - 1)
+            assert np.array_equal(ra, rb) and np.array_equal(sa, sb)
+    a.close(); b.close()
