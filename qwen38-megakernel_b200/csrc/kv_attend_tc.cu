@@ -25,6 +25,7 @@
 
 #include "kv_attend_common.cuh"
 #include "kv_kernels.h"
+#include "kv_merge.cuh"
 #include "kv_quant.cuh"
 #include "kv_unpack.h"
 
@@ -86,6 +87,8 @@ struct Args {
     unsigned long long * xb; // same shape: row maxima of the chunk up to and including the group
     int nbmax, epoch;
     int * status;
+    unsigned * done;        // fused merge: [kv head] count of CTAs whose partial is written, over all launches (wraps)
+    unsigned done_target;   // the count that means "every CTA of the head, this launch"; done == null: separate merge launch
     unsigned long long * prof; // optional: [CTA][16 groups][20] globaltimer stamps: softmax warp 0 (0 .. 7), unpack warp 8 (8 .. 15),
                                // issuer (16 .. 19)
 };
@@ -152,6 +155,11 @@ __device__ __forceinline__ unsigned desc_lo(unsigned addr, unsigned lbo) { retur
 __device__ __forceinline__ unsigned desc_hi(unsigned sbo) { return ((sbo >> 4) & 0x3fffu) | (1u << 14); }
 __device__ __forceinline__ void umma_commit(uint64_t * bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned * p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -760,6 +768,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         named_bar(5, NSOFT * 32);
         if (owner && q == 0 && r_own < R)
             a.ml[(size_t) slot * AR + r_own] = make_float2(m_acc, lsum[0][r_own] + lsum[1][r_own] + lsum[2][r_own] + lsum[3][r_own]);
+        if (a.done) {
+            // ---- the merge, in the kernel's tail: when every CTA of the kv head has written its partial, this CTA merges rows
+            // kk, kk + cph of the head's 6 T (one warp per row, as attn_merge_kernel) ----
+            __threadfence();
+            named_bar(5, NSOFT * 32);
+            if (warp == 0 && lane == 0) atomicAdd(a.done + g, 1u);
+            const int rr = kk + warp * a.cph;
+            if (warp < 2 && rr < GQ * T) {
+                bool ok = true;
+                if (lane == 0) {
+                    unsigned it = 0;
+                    while ((int) (ld_acquire_u32(a.done + g) - a.done_target) < 0) {
+                        __nanosleep(100);
+                        if (++it >= (1u << 23) || sm.dead) { // (about a second)
+                            atomicExch(a.status, (int) KS_WAIT_TIMEOUT);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                ok = __shfl_sync(FULL_MASK, ok, 0);
+                if (ok) merge_row(J, a.part, a.ml, (size_t) g * a.cph, 1, a.cph, g * GQ + rr / T, rr % T, lane, 0, nullptr, nullptr);
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -772,7 +804,8 @@ size_t attend_tc_smem_bytes() { return sizeof(tc::Smem) + 128; }
 
 cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, float2 * ml, int part_slots, unsigned long long * xa,
                              unsigned long long * xb, int nbmax, int epoch, int * status, cudaStream_t stream, const AttnTask * tasks_dev,
-                             int ntasks, int tasks_B, float * raw_part, float2 * raw_ml, unsigned long long * prof) {
+                             int ntasks, int tasks_B, float * raw_part, float2 * raw_ml, unsigned long long * prof, unsigned * done,
+                             unsigned * done_seq) {
     tc::Args a;
     a.prof = prof;
     a.one = job;
@@ -804,9 +837,17 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
+    // the merge runs in the kernel's tail unless the caller wants the un-normalised partials (a later merge across GPUs)
+    const bool fused = done && done_seq && !raw_part && job.O;
+    a.done = fused ? done : nullptr;
+    a.done_target = fused ? (*done_seq + 1u) * (unsigned) a.cph : 0u;
     void * args[] = {&a};
     e = cudaLaunchCooperativeKernel((const void *) tc::attn_tc_kernel, dim3(NKV * a.cph), dim3(tc::NTHREADS), args, attend_tc_smem_bytes(), stream);
     if (e != cudaSuccess) return e;
+    if (fused) {
+        *done_seq += 1u;
+        return cudaSuccess;
+    }
     AttnJob merge_job = job;
     merge_job.nch = a.cph; // the merge reads cph partials per kv head, slots g cph ..
     merge_job.item0 = 0;

@@ -116,6 +116,8 @@ KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
         use_tc_ = strcmp(c, "baseline") != 0 && strcmp(c, "fast") != 0;
     }
     ensure_xch(((cfg.ctx + ATT_BUCKET - 1) / ATT_BUCKET + 3) / 4 + 2);
+    MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&tc_done_), NKV * sizeof(unsigned)));
+    MKKV_CK(cudaMemset(tc_done_, 0, NKV * sizeof(unsigned)));
     if (const char * c = getenv("MK_KV_PROFILE"))
         if (atoi(c) > 0) {
             MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&prof_), attend_fast_prof_words(num_sms_) * sizeof(unsigned long long)));
@@ -144,9 +146,9 @@ void KvEngine::ensure_xch(int nb) {
 void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items, int max_T) {
     if (use_tc_ && njobs == 1) {
         const cudaError_t e = launch_attend_tc(jobs_host[0], num_sms_, part_, ml_, work_items_, xmax_, xmax_ + (size_t) NKV * ATT_NCH * xnb_ * AR,
-                                               xnb_, ++epoch_, d_status_, stream_, nullptr, 0, 0, nullptr, nullptr, prof_);
+                                               xnb_, ++epoch_, d_status_, stream_, nullptr, 0, 0, nullptr, nullptr, prof_, tc_done_, &tc_done_seq_);
         if (e == cudaSuccess) {
-            launches_ += 2;
+            launches_ += 1;
             return;
         }
         if (e != cudaErrorNotSupported && e != cudaErrorCooperativeLaunchTooLarge) MKKV_CK(e);
@@ -187,6 +189,7 @@ KvEngine::~KvEngine() {
     cudaFreeHost(h_tasks_);
     cudaFree(staging_);
     cudaFree(xmax_);
+    cudaFree(tc_done_);
     cudaFree(prof_);
     cudaFreeHost(h_status_);
     cudaEventDestroy(ev_compute_);

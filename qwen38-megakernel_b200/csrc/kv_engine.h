@@ -216,6 +216,8 @@ class KvEngine {
     int epoch_ = 0, num_sms_ = 0;
     bool use_fast_ = true, use_tc_ = true;
     int xnb_ = 0; // batches per chunk the exchange arrays hold
+    unsigned * tc_done_ = nullptr; // fused merge of the tensor-core kernel: per kv head, CTAs done over all launches
+    unsigned tc_done_seq_ = 0;     // launches that counted on it
     void ensure_xch(int nb);
     unsigned long long * prof_ = nullptr; // MK_KV_PROFILE=1: phase stamps of the last fast attention launch
     void launch_attention(const AttnJob * jobs_host, int njobs, int items, int max_T);

@@ -12,6 +12,7 @@
 
 #include "kv_kernels.h"
 #include "kv_quant.cuh"
+#include "kv_merge.cuh"
 
 namespace mkkv {
 
@@ -476,10 +477,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) attn_split_kernel(const __grid_c
     if (tid < R) a.ml[it * AR + tid] = make_float2(sm.m[tid], sm.l[tid]);
 }
 
-// merge of the chunk partials of one (query head, token): y = sum_c w_c O_c / sum_c w_c l_c, w_c = exp(m_c - max m), then the
-// inverse rotation when V is stored rotated (qwen38_mk.cu:4658-4685). One warp per row; lane holds dims 8 lane .. 8 lane + 7.
-// raw != 0: write the merged but un-normalised (m, l, O) of the row instead, as one partial per kv head (slot g of part_out /
-// ml_out, row (head % 6) T + t): the input of a later merge across GPUs
+// merge of the chunk partials of one (query head, token), one warp per row (kv_merge.cuh)
 __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__ AttnArgs a, int rows_per_job, int raw, float * part_out,
                                                          float2 * ml_out) {
     const int lane = threadIdx.x & 31, idx = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -487,49 +485,11 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__
     if (j >= (a.jobs ? a.njobs : 1)) return;
     const AttnJob & J = a.jobs ? a.jobs[j] : a.one;
     if (rr >= NH * J.T) return;
-    const int h = rr / J.T, t = rr % J.T, g = h / GQ, r = (h % GQ) * J.T + t;
+    const int h = rr / J.T, t = rr % J.T, g = h / GQ;
     const size_t i0 = (size_t) J.item0 + (J.pstride > 1 ? (size_t) g : (size_t) g * J.nch);
     const size_t cstep = J.pstride > 1 ? (size_t) J.pstride : 1; // slots between consecutive partials of the kv head
-    // lane c (and c + 32) holds partial c's (m, l): all weights first, so the sums below run over independent loads
-    float2 mla = lane < J.nch ? a.ml[(i0 + lane * cstep) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
-    float2 mlb = lane + 32 < J.nch ? a.ml[(i0 + (lane + 32) * cstep) * AR + r] : make_float2(-CUDART_INF_F, 0.f);
-    float M = fmaxf(mla.x, mlb.x);
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) M = fmaxf(M, __shfl_xor_sync(FULL, M, m));
-    const float wa = mla.x == -CUDART_INF_F ? 0.f : expf(mla.x - M), wb = mlb.x == -CUDART_INF_F ? 0.f : expf(mlb.x - M);
-    float num[8], den = 0.f;
-#pragma unroll
-    for (int k = 0; k < 8; k++) num[k] = 0.f;
-    const float * pbase = a.part + (i0 * AR + r) * HD + lane * 8;
-#pragma unroll 4
-    for (int c = 0; c < J.nch; c++) { // (partials beyond 64 per kv head do not occur: nch <= 20, or #SM / 4 for the fast path)
-        const float w = __shfl_sync(FULL, c < 32 ? wa : wb, c & 31), lc = __shfl_sync(FULL, c < 32 ? mla.y : mlb.y, c & 31);
-        const float4 * o = reinterpret_cast<const float4 *>(pbase + (size_t) c * cstep * AR * HD);
-        const float4 o0 = __ldcg(o), o1 = __ldcg(o + 1);
-        num[0] = __fmaf_rn(w, o0.x, num[0]);
-        num[1] = __fmaf_rn(w, o0.y, num[1]);
-        num[2] = __fmaf_rn(w, o0.z, num[2]);
-        num[3] = __fmaf_rn(w, o0.w, num[3]);
-        num[4] = __fmaf_rn(w, o1.x, num[4]);
-        num[5] = __fmaf_rn(w, o1.y, num[5]);
-        num[6] = __fmaf_rn(w, o1.z, num[6]);
-        num[7] = __fmaf_rn(w, o1.w, num[7]);
-        den = __fmaf_rn(w, lc, den);
-    }
-    if (raw) {
-        float4 * dst = reinterpret_cast<float4 *>(part_out + ((size_t) g * AR + r) * HD + lane * 8);
-        dst[0] = make_float4(num[0], num[1], num[2], num[3]);
-        dst[1] = make_float4(num[4], num[5], num[6], num[7]);
-        if (lane == 0) ml_out[(size_t) g * AR + r] = make_float2(M, den);
-        return;
-    }
-    float y[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) y[k] = __fdiv_rn(num[k], den);
-    if (J.kv.s[1].rot) fwht256(y, lane);
-    float4 * dst = reinterpret_cast<float4 *>(J.O + ((size_t) t * NH + h) * HD + lane * 8);
-    dst[0] = make_float4(y[0], y[1], y[2], y[3]);
-    dst[1] = make_float4(y[4], y[5], y[6], y[7]);
+    // (partials beyond 64 per kv head do not occur: nch <= 20, or #SM / 4 for the spread kernels)
+    merge_row(J, a.part, a.ml, i0, cstep, J.nch, h, t, lane, raw, part_out, ml_out);
 }
 
 cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,

@@ -52,10 +52,13 @@ size_t attend_fast_prof_words(int ctas);
 // Tensor-core path (kv_attend_tc.cu, tcgen05 + tensor memory): one job spread over num_sms CTAs in a cooperative launch, then the
 // merge. xa / xb: exchange arrays of [4][20][nbmax][48] 8-byte words each, zeroed once; epoch as for launch_attend_fast. A host-built
 // task list must use 4 tiles per batch (build_range_tasks with B = 4). cudaErrorNotSupported: shape not handled.
+// done (device, [4], zeroed once) + done_seq (host counter of launches that used it): the merge runs in the kernel's tail instead of
+// a second launch (not when raw_part is given).
 cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, float2 * ml, int part_slots, unsigned long long * xa,
                              unsigned long long * xb, int nbmax, int epoch, int * status, cudaStream_t stream,
                              const AttnTask * tasks_dev = nullptr, int ntasks = 0, int tasks_B = 0, float * raw_part = nullptr,
-                             float2 * raw_ml = nullptr, unsigned long long * prof = nullptr);
+                             float2 * raw_ml = nullptr, unsigned long long * prof = nullptr, unsigned * done = nullptr,
+                             unsigned * done_seq = nullptr);
 size_t attend_tc_smem_bytes();
 
 // batched append: job j writes n rows at pos0 of its own (sequence, layer)
