@@ -35,12 +35,29 @@ namespace tc {
 
 using namespace attn_common;
 
-constexpr int NSOFT = 8;   // softmax warps 0 .. 7: warp = 4 c2 + q, tile q (tensor-memory lanes 32 q ..), query rows 24 c2 .. + 23
-constexpr int NDQ = 16;    // unpack warps 8 .. 23: 4 c + q, tile q, dims 32 (4 h + c) .. + 31 of half h
+#ifndef MKKV_TC_NSL
+#define MKKV_TC_NSL 2 // row slices of the softmax warps: 3 (12 warps x 16 rows, 1024 threads) or 2 (8 warps x 24 rows, 896 threads)
+#endif
+constexpr int NSL = MKKV_TC_NSL;
+constexpr int NSOFT = 4 * NSL; // softmax warps first: warp = 4 c2 + q, tile q (tensor-memory lanes 32 q ..), query rows RS c2 .. + RS - 1
+constexpr int NDQ = 16;        // then the unpack warps: 4 c + q, tile q, dims 32 (4 h + c) .. + 31 of half h
 constexpr int W_ISSUE = NSOFT + NDQ, W_PROD = W_ISSUE + 1;
 constexpr int NTHREADS = (W_PROD + 3) * 32; // two idle warps complete the last group of four (register reallocation is per group)
 constexpr int GT = 4, GP = GT * ATP;        // tiles / positions per group: the M of one MMA
-constexpr int RS = AR / 2;                  // query rows per softmax warp
+constexpr int RS = AR / NSL;                // query rows per softmax warp
+// registers per thread after the reallocation (the launch gives 65536 / NTHREADS rounded down to 8; the three shares sum to at
+// most the CTA's launch allocation -- a larger sum faults)
+#if MKKV_TC_NSL == 3
+#define MKKV_TC_REGS_SOFT "80"
+#define MKKV_TC_REGS_DQ "56"
+#define MKKV_TC_REGS_CTL "40"
+static_assert(12 * 80 + 16 * 56 + 4 * 40 <= 32 * 64, "register shares");
+#else
+#define MKKV_TC_REGS_SOFT "112"
+#define MKKV_TC_REGS_DQ "56"
+#define MKKV_TC_REGS_CTL "56"
+static_assert(8 * 112 + 16 * 56 + 4 * 56 <= 28 * 72, "register shares");
+#endif
 constexpr int RAW_SLOT = ATP * HD + ATP * SCALE_ROW; // one tile of the widest format and its scales: 8704 bytes
 constexpr int NRAW = 9;
 constexpr int OP_SLOT = GP * 128 * 2;       // fp16 operand: 128 positions x 128 dims
@@ -164,20 +181,6 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned * p) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// 24 consecutive columns of the warp's 32 lanes (thread: lane, 24 values)
-__device__ __forceinline__ void tmem_ld24(unsigned taddr, float (&v)[RS]) {
-    unsigned r[RS];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23])
-                 : "r"(taddr + 16));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < RS; i++) v[i] = __uint_as_float(r[i]);
-}
 // 8 consecutive columns, in flight until tmem_wait8 on the same registers (the wait names them so that no use can move above it)
 __device__ __forceinline__ void tmem_ld8_async(unsigned taddr, unsigned (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -202,18 +205,6 @@ __device__ __forceinline__ void tmem_st8(unsigned taddr, const float (&v)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(__float_as_uint(v[0])),
                  "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])),
                  "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7]))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st24(unsigned taddr, const float (&v)[RS]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-                 "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-                 "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-                 "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-                 "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
-                 : "memory");
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr + 16), "r"(__float_as_uint(v[16])),
-                 "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
-                 "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23]))
                  : "memory");
 }
 #ifndef MKKV_TC_EXPF
@@ -395,9 +386,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const unsigned tb = sm.tmem_base;
-    // registers move from the unpack / control warps to the softmax warps (72 each at launch)
-    if (warp >= NSOFT) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    // registers move from the unpack / control warps to the softmax warps
+    if (warp >= W_ISSUE) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 " MKKV_TC_REGS_CTL ";");
     if (warp == W_PROD) {
         // ---- producer: K(0), K(1), K(2), then V(i), K(i + 3) -- the order the unpack warps consume ----
         if (lane == 0) {
@@ -472,7 +463,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 }
             }
         }
-    } else if (warp >= NSOFT && warp < W_ISSUE) {
+    }
+    } else if (warp >= NSOFT) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 " MKKV_TC_REGS_DQ ";");
         // ---- unpack warps: packed rows -> operand slots, both 128-dim halves of one side of a group at a time ----
         const int w = warp - NSOFT, q = w & 3, c = w >> 2, prow = ATP * q + lane;
         const unsigned pos_off = (prow >> 3) * 128 + (prow & 7) * 16; // the position's 16-byte unit inside a dim group
@@ -512,9 +505,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             if (isK) nk++;
             else nv++;
         }
-    }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 " MKKV_TC_REGS_SOFT ";");
         // ---- softmax warps: warp = 4 c2 + q: positions 32 q .. + 31 of a group (tensor-memory lanes 32 q ..), query rows
         // 24 c2 .. + 23. Lanes 0 .. 23 own one row each (its running / reference max; replicated over the four q) ----
         const int q = warp & 3, c2 = warp >> 2, prow = ATP * q + lane, row0 = RS * c2;
@@ -562,15 +554,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             const Task k = sm.tasks[j & 7];
             if (st) TC_STAMP(j, 1);
             tc_fence_after();
-            unsigned ra[8], rb[8], rc[8];
-            scores_request(j, 0, ra);
-            scores_request(j, 1, rb);
-            scores_request(j, 2, rc);
+            unsigned rq[RS / 8][8];
+#pragma unroll
+            for (int gq = 0; gq < RS / 8; gq++) scores_request(j, gq, rq[gq]);
             const unsigned mask = row_mask(k);
 #pragma unroll
             for (int gq = 0; gq < RS / 8; gq++) {
                 float s[8];
-                scores_take(gq == 0 ? ra : gq == 1 ? rb : rc, mask, gq, s);
+                scores_take(rq[gq], mask, gq, s);
                 int kx[8];
 #pragma unroll
                 for (int i = 0; i < 8; i++) kx[i] = __reduce_max_sync(FULL_MASK, f2key(s[i]));
@@ -672,8 +663,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             unsigned ra[8], rb[8];
             scores_request(i, 0, ra);
 #pragma unroll
-            for (int gq = 0; gq < RS / 8; gq++) { // three row groups of 8: one 16-byte unit of each P part; the next group's
-                                                  // scores are in flight while this one's P is computed
+            for (int gq = 0; gq < RS / 8; gq++) { // row groups of 8: one 16-byte unit of each P part; the next group's scores are in
+                                                  // flight while this one's P is computed
                 float s[8];
                 if (gq + 1 < RS / 8) {
                     if (gq & 1) {
