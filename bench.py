@@ -256,6 +256,155 @@ def run_split(args):
         dist.destroy_process_group()
 
 
+def run_config3(args):
+    """Config 3: 32 independent sequences of log-uniform length [2,000, 100,000], 1..8 tokens each per step, 16 layers, dealt to
+    the GPUs longest-first by KV bytes (no collective). A step is one batched launch sequence per layer over the rank's
+    sequences; the metric is the whole job's tokens per second."""
+    import numpy as np
+    import torch
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    mk = importlib.import_module("qwen38-megakernel_b200")
+    mk.load_library()
+    layers, NS = args.layers, 32
+    rng = np.random.default_rng(3)
+    lens = np.exp(rng.uniform(np.log(2000), np.log(100000), size=NS)).astype(np.int64)
+    Ts = rng.integers(1, T_STEP + 1, size=NS)
+    mine = mk.parallel.lpt_partition([int(x) for x in lens], world)[rank]
+    total_steps = args.warmup + args.steps + 2
+    cap = int(max(lens[i] for i in mine)) + total_steps * T_STEP + 64
+    stream = torch.cuda.current_stream()
+    eng = mk.Engine(layers, 64, SPEC, WIN, spill=not args.eager, stream=stream)
+    eng.slots_open(len(mine), cap)
+    eng.reserve_batch(len(mine))
+    g = torch.Generator(device="cuda")
+    g.manual_seed(300 + rank)
+    for si, i in enumerate(mine):
+        for l in range(layers):
+            for a in range(0, int(lens[i]), 16384):
+                m = min(16384, int(lens[i]) - a)
+                K = (torch.randn((m, NKV, HD), generator=g, device="cuda") * 1.3).half()
+                V = (torch.randn((m, NKV, HD), generator=g, device="cuda") * 1.3).half()
+                eng.append(l, a, K, V, seq=si)
+    n = [int(lens[i]) for i in mine]
+    T = [int(Ts[i]) for i in mine]
+    sumT = sum(T)
+    K = (torch.randn((layers, sumT, NKV, HD), generator=g, device="cuda") * 1.3).half()
+    V = (torch.randn((layers, sumT, NKV, HD), generator=g, device="cuda") * 1.3).half()
+    Q = torch.randn((layers, sumT, NH, HD), generator=g, device="cuda").half()
+    O = torch.empty((layers, sumT, NH, HD), dtype=torch.float32, device="cuda")
+    seqs = list(range(len(mine)))
+    state = {"n": n}
+
+    def one_step():
+        nn = state["n"]
+        Tc = [mk.cap_T(a, t) for a, t in zip(nn, T)]
+        for l in range(layers):
+            eng.step_batch(seqs, l, nn, T, K[l], V[l], Q[l], O[l]) if Tc == T else eng.step_batch(seqs, l, nn, Tc, K[l], V[l], Q[l], O[l])
+        state["n"] = [a + t for a, t in zip(nn, Tc)]
+        return sum(Tc)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    toks = 0
+    for _ in range(args.steps):
+        toks += one_step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    tot = torch.tensor([ms, float(toks)], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        mx = tot.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm_ = tot.clone(); dist.all_reduce(sm_, op=dist.ReduceOp.SUM)
+        ms, toks = float(mx[0]), float(sm_[1])
+    if rank == 0:
+        print(json.dumps({"metric": "aggregate_decode_tokens_per_s", "value": toks / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "f16 operands / f32 accumulate over u8 packed 5/6/8-bit rows", "data": "synthetic",
+                          "config": {"workload": "config3: 32 sequences, lengths log-uniform [2,000, 100,000], 1..8 tokens each per step, %d attention "
+                                                 "layers (attention + KV append only), dealt to the GPUs longest-first by KV bytes" % layers,
+                                     "kv_spec": SPEC, "kv_win": WIN, "positions_total": int(lens.sum()), "tokens_per_step": int(Ts.sum())},
+                          "clocks": clocks}))
+    eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_config4(args):
+    """Config 4: 100,000 positions x 16 layers parked in pinned host memory, the first 11,700 restored, 2,000 rows appended,
+    8 tokens decoded. The metric is the restore rate (GB/s of KV rows brought back, host -> device)."""
+    import torch
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    torch.cuda.set_device(local_rank)
+    mk = importlib.import_module("qwen38-megakernel_b200")
+    mk.load_library()
+    layers, L, P, A = args.layers, 100000, 11700, 2000
+    eng = mk.Engine(layers, L + 64, SPEC, WIN, spill=not args.eager)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    for l in range(layers):
+        for a in range(0, L, 20000):
+            K = (torch.randn((20000, NKV, HD), generator=g, device="cuda") * 1.3).half()
+            V = (torch.randn((20000, NKV, HD), generator=g, device="cuda") * 1.3).half()
+            eng.append(l, a, K, V)
+    eng.commit(L)
+    eng.store_budget(4 << 30)
+    eng.store_reserve(eng.park_need())  # the pinned chunks exist before the timed park
+    eng.sync()
+    t0 = time.perf_counter()
+    pid = eng.park()
+    eng.sync()
+    t_park = time.perf_counter() - t0
+    nbytes = eng.park_bytes(pid)
+    row_bytes = layers * NKV * ((32 * 5 + 16) + (32 * 6 + 16))
+    rates = []
+    for _ in range(max(args.steps, 1) if args.steps < 16 else 5):
+        eng.reset()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.restore_prefix(pid, P, wait=True)
+        eng.sync()
+        rates.append(P * row_bytes / (time.perf_counter() - t0) / 1e9)
+    Kn = (torch.randn((A, NKV, HD), generator=g, device="cuda") * 1.3).half()
+    Q = torch.randn((T_STEP, NH, HD), generator=g, device="cuda").half()
+    O = torch.empty((T_STEP, NH, HD), dtype=torch.float32, device="cuda")
+    t0 = time.perf_counter()
+    for l in range(layers):
+        eng.append(l, P, Kn, Kn)
+    n = P + A - T_STEP
+    eng.commit(n)
+    for l in range(layers):
+        eng.attend(l, n, Q, O)
+    eng.sync()
+    t_tail = time.perf_counter() - t0
+    print(json.dumps({"metric": "kv_restore_gb_per_s", "value": max(rates), "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "vs_baseline": None,
+                      "data": "synthetic", "dtype": "u8 packed rows",
+                      "config": {"workload": "config4: park 100,000 positions x %d layers (%0.2f GB with the rings), restore positions [0, 11,700) "
+                                             "(%0.1f MB of rows), append 2,000 rows, decode 8 tokens" % (layers, nbytes / 1e9, P * row_bytes / 1e6),
+                                 "kv_spec": SPEC, "kv_win": WIN},
+                      "park_gb_per_s": nbytes / t_park / 1e9, "restore_gb_per_s_runs": rates, "reappend_plus_decode_ms": 1e3 * t_tail,
+                      "bound": "host link (PCIe, pinned memory)"}))
+    eng.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -267,12 +416,17 @@ def main():
     ap.add_argument("--eager", action="store_true", help="dual-write every row at append instead of spilling on eviction")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--split-ctx", type=int, default=0, help="config 2b: one sequence of this many positions split over the GPUs")
+    ap.add_argument("--config", type=int, default=2, help="2 (default): the headline decode workload; 3: 32 sequences dealt to the GPUs; 4: snapshot / restore")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else max(args.warmup, 1)
     if args.impl == "reference":
         return run_reference(args)
     if args.split_ctx > 0:
         return run_split(args)
+    if args.config == 3:
+        return run_config3(args)
+    if args.config == 4:
+        return run_config4(args)
 
     import numpy as np
     import torch
