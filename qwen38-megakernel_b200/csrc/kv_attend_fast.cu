@@ -672,6 +672,14 @@ template <int MT> static cudaError_t fast_launch_mt(const fast::Args & a, int gr
     return cudaGetLastError();
 }
 
+cudaError_t preload_attend_fast() {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, (const void *) fast::attn_fast_kernel<1>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, (const void *) fast::attn_fast_kernel<2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, (const void *) fast::attn_fast_kernel<3>);
+    return e;
+}
+
 cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, int num_sms,
                                float * part, float2 * ml, int part_slots, unsigned long long * xmax, int nbmax, int epoch, int * status,
                                unsigned long long * prof, bool spread, cudaStream_t stream, const AttnTask * tasks_dev, int ntasks,

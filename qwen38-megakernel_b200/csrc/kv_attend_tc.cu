@@ -96,6 +96,8 @@ struct Smem {
 
 struct Args {
     AttnJob one;
+    const AttnJob * jobs;   // batch mode: device array of njobs jobs, one CTA per (job, kv head, chunk); else null: one job spread
+    int njobs;              // over cph CTAs per kv head with the exchange of row maxima
     int cph, ntasks;        // CTAs per kv head; tasks per kv head when a host-built list is given
     const AttnTask * tasks; // optional list (position-range jobs)
     float * part;           // [CTA][AR][HD]
@@ -328,7 +330,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
     Smem & sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t) 127);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     {
-        const unsigned * src = reinterpret_cast<const unsigned *>(&a.one);
+        const AttnJob * Jp = &a.one;
+        if (a.jobs) { // batch mode: the job whose items contain this CTA
+            int j = 0;
+            while (j + 1 < a.njobs && (int) blockIdx.x >= a.jobs[j + 1].item0) j++;
+            Jp = &a.jobs[j];
+        }
+        const unsigned * src = reinterpret_cast<const unsigned *>(Jp);
         unsigned * dst = reinterpret_cast<unsigned *>(&sm.job);
         for (int i = tid; i < (int) (sizeof(AttnJob) / 4); i += NTHREADS) dst[i] = src[i];
     }
@@ -348,16 +356,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
     __syncthreads();
     const AttnJob & J = sm.job;
     const KvView & kv = J.kv;
-    const int g = blockIdx.x / a.cph, kk = blockIdx.x % a.cph, slot = blockIdx.x;
+    // spread mode: CTA kk of kv head g runs tasks kk, kk + cph, .. of the head; batch mode: the CTA runs the groups of chunk c_fixed
+    // of kv head g of its job in order (task t = group t), the running max carried from group to group in registers
+    const bool batch = a.jobs != nullptr;
+    const int item = batch ? (int) blockIdx.x - J.item0 : 0;
+    const int g = batch ? item / J.nch : (int) blockIdx.x / a.cph, kk = batch ? 0 : (int) blockIdx.x % a.cph, slot = blockIdx.x;
+    const int c_fixed = batch ? item % J.nch : 0, tstep = batch ? 1 : a.cph;
     const int T = J.T, n = J.n, R = GQ * T, ws = J.ws;
     Geo4 geo4;
     geo4.g = make_geo(J, GT);
     geo4.mul_nch = geo4.g.nch > 1 ? 0xffffffffu / (unsigned) geo4.g.nch + 1u : 0u;
     geo4.mul_nch1 = geo4.g.nch > 2 ? 0xffffffffu / (unsigned) (geo4.g.nch - 1) + 1u : 0u;
     const AttnTask * const ttab = a.tasks;
-    const int t_end = ttab ? a.ntasks : geo4.g.ntasks_head;
-    auto get_task = [&](int t) -> Task { return ttab ? ttab[t] : make_task4(geo4, t); };
-    const int G = kk < t_end ? (t_end - kk + a.cph - 1) / a.cph : 0; // this CTA's groups: tasks kk, kk + cph, ..
+    const int t_end = batch ? ((c_fixed == geo4.g.nch - 1 ? geo4.g.nt_last : geo4.g.nt_full) + GT - 1) / GT : ttab ? a.ntasks : geo4.g.ntasks_head;
+    auto get_task = [&](int t) -> Task { return batch ? make_task(geo4.g, GT, 1, t, c_fixed) : ttab ? ttab[t] : make_task4(geo4, t); };
+    const int G = kk < t_end ? (t_end - kk + tstep - 1) / tstep : 0; // this CTA's groups: tasks kk, kk + tstep, ..
 
     // query rows of the kv head: fp16 -> fp32 -> (K's rotation) -> x 1/16 -> fp16 (qwen38_mk.cu:2876-2883), row = (head % 6) T + t,
     // as the K-major B operand: lane holds dims 8 lane .. + 7 = one 16-byte unit
@@ -399,7 +412,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 Task k;
                 if (isK) { // a group's K comes first: its task is computed here, once, and left for the other roles (the waits on
                            // the copies' barriers order their reads after this write)
-                    k = get_task(kk + nk * a.cph);
+                    k = get_task(kk + nk * tstep);
                     sm.tasks[nk & 7] = k;
                 } else {
                     k = sm.tasks[nv & 7];
@@ -518,7 +531,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         float l_acc[RS];
 #pragma unroll
         for (int i = 0; i < RS; i++) l_acc[i] = 0.f;
-        float m_acc = -CUDART_INF_F;
+        float m_acc = -CUDART_INF_F, carry = -CUDART_INF_F; // (carry: batch mode, the chunk's running max after the previous group)
         unsigned long long w0 = 0, w1 = 0, w2 = 0;
         auto xbase = [&](const Task & k) -> size_t { return (((size_t) g * ATT_NCH + k.c) * a.nbmax) * AR + r_own; };
         // which of the warp's rows this thread's position must not see in group k: row token t sees positions <= n + t; positions
@@ -572,7 +585,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 }
             }
             named_bar(1 + c2, GT * 32);
-            if (owner && q == 0 && k.nb > 1 && k.b + 1 < k.nb) {
+            if (!batch && owner && q == 0 && k.nb > 1 && k.b + 1 < k.nb) {
                 const int(&tm)[GT][AR] = sm.tmax[j % 3];
                 const int gk = max(max(tm[0][r_own], tm[1][r_own]), max(tm[2][r_own], tm[3][r_own]));
                 __stcg(a.xa + xbase(k) + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(key2f(gk)));
@@ -582,7 +595,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         // the words the running max of group k will need: requested one phase before they are used, when the CTAs that hold
         // the chunk's previous groups have most likely published them
         auto request_words = [&](const Task & k) {
-            if (owner && k.nb > 1) {
+            if (!batch && owner && k.nb > 1) {
                 const size_t xb0 = xbase(k);
                 if (k.b >= 1) w1 = __ldcv(a.xa + xb0 + (size_t) (k.b - 1) * AR);
                 if (k.b >= 2) w2 = __ldcv(a.xa + xb0 + (size_t) (k.b - 2) * AR);
@@ -594,9 +607,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             if (st) TC_STAMP(i, 3);
             float beta = 0.f, f = 1.f;
             if (owner) {
-                float m_in = -CUDART_INF_F;
+                float m_in = batch && k.b > 0 ? carry : -CUDART_INF_F;
                 const size_t xb0 = xbase(k);
-                if (k.nb > 1) {
+                if (!batch && k.nb > 1) {
                     if (k.b >= 1) m_in = poll_word(a.xa + xb0 + (size_t) (k.b - 1) * AR, w1, a.epoch, a.status);
                     if (k.b >= 2) m_in = fmaxf(m_in, poll_word(a.xa + xb0 + (size_t) (k.b - 2) * AR, w2, a.epoch, a.status));
                     if (k.b >= 3) m_in = fmaxf(m_in, poll_word(a.xb + xb0 + (size_t) (k.b - 3) * AR, w0, a.epoch, a.status));
@@ -612,7 +625,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 for (int t = 0; t < GT; t++)
                     if (t > q) kM = max(kM, tm[t][r_own]);
                 const float mr = key2f(kr), M = key2f(kM);
-                if (q == 0 && k.nb > 1 && k.b + 3 < k.nb) __stcg(a.xb + xb0 + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(M));
+                if (!batch && q == 0 && k.nb > 1 && k.b + 3 < k.nb) __stcg(a.xb + xb0 + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(M));
+                carry = M;
                 if (M != -CUDART_INF_F) {
                     if (m_acc == -CUDART_INF_F) m_acc = M + REF_MARGIN;
                     else if (M > m_acc + REF_SLACK) {
@@ -792,6 +806,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
 } // namespace tc
 
 size_t attend_tc_smem_bytes() { return sizeof(tc::Smem) + 128; }
+cudaError_t preload_attend_tc() {
+    cudaFuncAttributes fa;
+    return cudaFuncGetAttributes(&fa, (const void *) tc::attn_tc_kernel);
+}
 
 cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, float2 * ml, int part_slots, unsigned long long * xa,
                              unsigned long long * xb, int nbmax, int epoch, int * status, cudaStream_t stream, const AttnTask * tasks_dev,
@@ -800,6 +818,8 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
     tc::Args a;
     a.prof = prof;
     a.one = job;
+    a.jobs = nullptr;
+    a.njobs = 1;
     a.cph = num_sms / NKV;
     if (a.cph < 1 || a.cph > 64 || NKV * a.cph > part_slots) return cudaErrorNotSupported; // (the merge keeps a head's weights in two registers per lane)
     a.tasks = nullptr;
@@ -843,6 +863,42 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
     merge_job.nch = a.cph; // the merge reads cph partials per kv head, slots g cph ..
     merge_job.item0 = 0;
     return launch_merge(nullptr, &merge_job, 1, job.T, part, ml, stream, raw_part, raw_ml);
+}
+
+// Batch mode: njobs jobs, one CTA per (job, kv head, chunk) item in a plain launch (no CTA waits for another: the groups of a chunk
+// run in order on one CTA), then the merge kernel over the jobs' partials (slot = item).
+cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
+                                   float2 * ml, int part_slots, int * status, cudaStream_t stream) {
+    if (njobs < 1 || total_items < 1 || total_items > part_slots || !jobs_dev) return cudaErrorNotSupported;
+    tc::Args a;
+    a.one = jobs_host[0];
+    a.jobs = jobs_dev;
+    a.njobs = njobs;
+    a.cph = 1;
+    a.ntasks = 0;
+    a.tasks = nullptr;
+    a.part = part;
+    a.ml = ml;
+    a.xa = a.xb = nullptr;
+    a.nbmax = 0;
+    a.epoch = 0;
+    a.status = status;
+    a.done = nullptr;
+    a.done_target = 0;
+    a.prof = nullptr;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !attr_set[dev]) {
+        e = cudaFuncSetAttribute(tc::attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) attend_tc_smem_bytes());
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    tc::attn_tc_kernel<<<total_items, tc::NTHREADS, attend_tc_smem_bytes(), stream>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return launch_merge(jobs_dev, jobs_host, njobs, max_T, part, ml, stream);
 }
 
 } // namespace mkkv

@@ -110,6 +110,7 @@ KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
         if (v >= 1 && v <= 1024) hs_chunk_ = (size_t) v << 20;
     }
     MKKV_CK(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, dev_));
+    MKKV_CK(preload_kernels());
     // MK_KV_ATTN: "tc" (default: tensor-core kernel, the others as fallbacks), "fast" (no tcgen05 kernel), "baseline" (the simple kernel only)
     if (const char * c = getenv("MK_KV_ATTN")) {
         use_fast_ = strcmp(c, "baseline") != 0;
@@ -152,6 +153,15 @@ void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items,
             return;
         }
         if (e != cudaErrorNotSupported && e != cudaErrorCooperativeLaunchTooLarge) MKKV_CK(e);
+        cudaGetLastError();
+    }
+    if (use_tc_ && njobs > 1) {
+        const cudaError_t e = launch_attend_tc_batch(d_jobs_, jobs_host, njobs, items, max_T, part_, ml_, work_items_, d_status_, stream_);
+        if (e == cudaSuccess) {
+            launches_ += 2;
+            return;
+        }
+        if (e != cudaErrorNotSupported) MKKV_CK(e);
         cudaGetLastError();
     }
     if (use_fast_) {

@@ -539,6 +539,24 @@ cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, in
 static __device__ __align__(256) float g_static_part[(size_t) STATIC_ITEMS * AR * HD];
 static __device__ __align__(256) float2 g_static_ml[(size_t) STATIC_ITEMS * AR];
 
+// Loads the library's kernels on the current device now (the runtime loads a kernel's code at its first launch otherwise, which
+// takes device memory at that moment): after this, no launch of this library allocates anything.
+cudaError_t preload_kernels() {
+    cudaFuncAttributes fa;
+    const void * fns[] = {(const void *) append_kernel, (const void *) spill_kernel, (const void *) refill_kernel, (const void *) append_batch_kernel,
+                          (const void *) gather_kernel, (const void *) attn_split_kernel, (const void *) attn_merge_kernel};
+    for (const void * f : fns) {
+        const cudaError_t e = cudaFuncGetAttributes(&fa, f);
+        if (e != cudaSuccess) return e;
+    }
+    void * p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_part);
+    if (e != cudaSuccess) return e;
+    e = preload_attend_fast();
+    if (e != cudaSuccess) return e;
+    return preload_attend_tc();
+}
+
 cudaError_t launch_attend_static(const AttnJob & job, int * status, cudaStream_t stream) {
     static float * part_addr[64] = {};
     static float2 * ml_addr[64] = {};
