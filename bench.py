@@ -275,6 +275,7 @@ def run_config3(args):
     lens = np.exp(rng.uniform(np.log(2000), np.log(100000), size=NS)).astype(np.int64)
     Ts = rng.integers(1, T_STEP + 1, size=NS)
     mine = mk.parallel.lpt_partition([int(x) for x in lens], world)[rank]
+    mine.sort(key=lambda i: -int(lens[i]))  # longest first: their CTAs (one per chunk, 4 x 20 per sequence) start first
     total_steps = args.warmup + args.steps + 2
     cap = int(max(lens[i] for i in mine)) + total_steps * T_STEP + 64
     stream = torch.cuda.current_stream()

@@ -535,24 +535,33 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
     std::vector<AttnTask> tasks;
     bool tc = use_tc_;
     for (;; tc = false) { // the tensor-core kernel first (4 tiles per task), else the fast kernel (8)
-        const int B = tc ? 4 : 8, max_nb = build_range_tasks(j, B, tasks);
-        if (tc) ensure_xch(max_nb);
-        else if (max_nb > std::min(xnb_, 64)) throw std::runtime_error("attend_partial: the context is too long for the exchange buffers");
-        const int nt = (int) tasks.size();
-        if (nt > tasks_cap_) {
-            MKKV_CK(cudaStreamSynchronize(stream_));
-            cudaFree(d_tasks_);
-            cudaFreeHost(h_tasks_);
-            d_tasks_ = nullptr;
-            h_tasks_ = nullptr;
-            tasks_cap_ = std::max(nt, 4096);
-            MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&d_tasks_), sizeof(AttnTask) * tasks_cap_));
-            MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&h_tasks_), sizeof(AttnTask) * tasks_cap_, cudaHostAllocDefault));
+        // the task list depends on the partition and the range only: a rank whose range does not end at the context's end keeps
+        // the list of the previous step (no rebuild, no upload)
+        const int B = tc ? 4 : 8;
+        const long long key[5] = {j.nch, j.cs, pos_lo, pos_hi, B};
+        int nt = tasks_n_;
+        if (memcmp(key, tasks_key_, sizeof(key)) != 0 || tasks_n_ < 0) {
+            const int max_nb = build_range_tasks(j, B, tasks);
+            if (tc) ensure_xch(max_nb);
+            else if (max_nb > std::min(xnb_, 64)) throw std::runtime_error("attend_partial: the context is too long for the exchange buffers");
+            nt = (int) tasks.size();
+            if (nt > tasks_cap_) {
+                MKKV_CK(cudaStreamSynchronize(stream_));
+                cudaFree(d_tasks_);
+                cudaFreeHost(h_tasks_);
+                d_tasks_ = nullptr;
+                h_tasks_ = nullptr;
+                tasks_cap_ = std::max(nt, 4096);
+                MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&d_tasks_), sizeof(AttnTask) * tasks_cap_));
+                MKKV_CK(cudaHostAlloc(reinterpret_cast<void **>(&h_tasks_), sizeof(AttnTask) * tasks_cap_, cudaHostAllocDefault));
+            }
+            MKKV_CK(cudaEventSynchronize(ev_compute_)); // the previous upload has been consumed
+            if (nt) memcpy(h_tasks_, tasks.data(), sizeof(AttnTask) * nt);
+            if (nt) MKKV_CK(cudaMemcpyAsync(d_tasks_, h_tasks_, sizeof(AttnTask) * nt, cudaMemcpyHostToDevice, stream_));
+            MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+            memcpy(tasks_key_, key, sizeof(key));
+            tasks_n_ = nt;
         }
-        MKKV_CK(cudaEventSynchronize(ev_compute_)); // the previous call's upload has been consumed
-        if (nt) memcpy(h_tasks_, tasks.data(), sizeof(AttnTask) * nt);
-        if (nt) MKKV_CK(cudaMemcpyAsync(d_tasks_, h_tasks_, sizeof(AttnTask) * nt, cudaMemcpyHostToDevice, stream_));
-        MKKV_CK(cudaEventRecord(ev_compute_, stream_));
         cudaError_t e;
         if (tc)
             e = launch_attend_tc(j, num_sms_, part_, ml_, work_items_, xmax_, xmax_ + (size_t) NKV * ATT_NCH * xnb_ * AR, xnb_, ++epoch_, d_status_,

@@ -209,6 +209,8 @@ class KvEngine {
     AttnTask * d_tasks_ = nullptr; // task list of a position-range job
     AttnTask * h_tasks_ = nullptr; // pinned
     int tasks_cap_ = 0;
+    long long tasks_key_[5] = {-1, -1, -1, -1, -1}; // (partition, range, tiles per task) of the list d_tasks_ holds
+    int tasks_n_ = -1;
     int * h_status_ = nullptr; // mapped pinned word the kernels write
     int * d_status_ = nullptr;
     // fast attention path: exchange of row maxima between the CTAs of one chunk
