@@ -8,6 +8,10 @@ that left the window into the 5/6-bit tier) and run decode attention of 8 query 
 the positions are committed. N > 1 (torchrun): every rank streams its own sequence (independent sequence slots, no
 collective). Prints one JSON line (rank 0).
 
+Side modes (not the headline): --split-ctx L (config 2b: one sequence of L positions split by position over the ranks, NCCL
+combine), --config 3 (32 sequences dealt to the ranks, whole-job tokens/s), --config 4 (snapshot / restore of 100,000 positions,
+GB/s).
+
 --impl reference times the CPU restatement of the reference's kernels (the parity oracle) on the host cores: the reference
 engine has no CPU implementation of this path, and its CUDA kernels need its whole model runtime.
 """

@@ -156,13 +156,12 @@ __device__ __forceinline__ void tc_wait(uint64_t * bar, unsigned parity, volatil
 }
 
 // ---- tcgen05 ----
-__device__ __forceinline__ uint64_t smem_desc(unsigned addr, unsigned lbo, unsigned sbo) { // no swizzle, version 1
-    return (uint64_t) ((addr >> 4) & 0x3fffu) | ((uint64_t) ((lbo >> 4) & 0x3fffu) << 16) | ((uint64_t) ((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
-}
+// Shared-memory matrix descriptors (no swizzle, version 1), as their 32-bit halves: the low half holds the start address and the
+// byte distance between the two 8-element groups along K of one instruction ("leading"), the high half the distance between 8-row
+// groups along M / N ("stride"). Only the low half changes between k-steps.
 // D[128 x 48] (+)= A B, fp16 operands, fp32 accumulate; MN: both operands MN-major, else both K-major
 constexpr unsigned IDESC_K = (1u << 4) | ((unsigned) (AR / 8) << 17) | ((unsigned) (GP / 16) << 24);
 constexpr unsigned IDESC_MN = (1u << 4) | (1u << 15) | (1u << 16) | ((unsigned) (2 * AR / 8) << 17) | ((unsigned) (GP / 16) << 24); // N = 96
-// (descriptors as their 32-bit halves: only the low half, which holds the start address, changes between k-steps)
 __device__ __forceinline__ void umma(unsigned d_tmem, unsigned a_lo, unsigned a_hi, unsigned b_lo, unsigned b_hi, unsigned idesc, unsigned accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\tsetp.ne.b32 p, %6, 0;\n\t"
@@ -488,6 +487,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         for (int nk = 0, nv = 0; nv < G;) {
             const bool isK = nk < G && nk < nv + NSB;
             const int side = isK ? 0 : 1, grp = isK ? nk - NSB : nv;
+            (void) grp; // (the stamps' group index)
             if (st) TC_STAMP(grp, side ? 8 : 11);
             tc_wait(&sm.raw_full[rs], rph, &sm.dead, a.status);
             if (st) TC_STAMP(grp, side ? 9 : 12);
