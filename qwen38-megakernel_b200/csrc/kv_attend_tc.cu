@@ -15,9 +15,13 @@
 //     exchange the running max with the CTAs that hold the chunk's earlier groups through small global arrays (own group
 //     maxima and cumulative maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as
 //     the B operand. The accumulator is kept against a per-row reference max that moves rarely (when the running max passes
-//     it by more than 8): P, after its fp16 rounding, is multiplied by exp(running max - reference) and carried as an fp16
-//     high and low part (two MMAs), so the reference's fp16 P is reproduced and no per-tile accumulator rescale is needed;
-//   - a CTA writes one un-normalised partial (m, l, O); attn_merge_kernel combines them.
+//     it by more than 10.5): P, after its fp16 rounding, is multiplied by exp(running max - reference) and carried as an fp16
+//     high and low part (one N = 96 MMA per k-step, two 48-column accumulator blocks), so the reference's fp16 P is reproduced
+//     and no per-tile accumulator rescale is needed;
+//   - a CTA writes one un-normalised partial (m, l, O); when the CTAs of a kv head have all written theirs (arrival count,
+//     bounded wait) each merges one or two of the head's rows in the kernel's tail (merge_row);
+//   - batch mode (several jobs): one CTA per (job, kv head, chunk) in a plain launch, the chunk's groups in order on that CTA with
+//     the running max carried in registers; attn_merge_kernel afterwards.
 // Every wait is bounded (about two seconds), then the status word is set and the kernel runs to its end and frees its
 // tensor memory.
 #include <cuda_fp16.h>

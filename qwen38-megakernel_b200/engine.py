@@ -206,9 +206,14 @@ class Engine:
         self._ck(self.L.mk_kv_step(self.h, seq, layer, n, Q.shape[0], _ptr(K), _ptr(V), _ptr(Q), _ptr(O)), "step")
 
     def step_layers(self, n, K, V, Q, O, seq=SEQ_MAIN):
-        """one decode step over every layer in one call: K, V [layers][T][4][256], Q [layers][T][24][256], O likewise (fp32)"""
-        self._ck(self.L.mk_kv_step_layers(self.h, seq, K.shape[0], n, Q.shape[1], _ptr(K), _ptr(V), _ptr(Q), _ptr(O), K.stride(0) * K.element_size(),
-                                          Q.stride(0) * Q.element_size(), O.stride(0) * O.element_size()), "step_layers")
+        """one decode step over every layer in one call: K, V [layers][T][4][256], Q [layers][T][24][256], O likewise (fp32).
+        A layer's rows must be contiguous; the layer stride is free (the first T rows of a larger per-layer buffer are fine)."""
+        for x in (K, V, Q, O):
+            if not x.is_cuda or not x[0].is_contiguous():
+                raise EngineError("step_layers: expected CUDA tensors whose per-layer rows are contiguous")
+        self._ck(self.L.mk_kv_step_layers(self.h, seq, K.shape[0], n, Q.shape[1], K.data_ptr(), V.data_ptr(), Q.data_ptr(), O.data_ptr(),
+                                          K.stride(0) * K.element_size(), Q.stride(0) * Q.element_size(), O.stride(0) * O.element_size()),
+                 "step_layers")
 
     def reserve_batch(self, njobs):
         self._ck(self.L.mk_kv_reserve_batch(self.h, njobs), "reserve_batch")

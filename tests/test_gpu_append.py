@@ -168,6 +168,10 @@ def test_step_layers_equals_per_layer_steps(mk, torch_cuda):
     a.step_layers(L, Ks, Vs, Qs, Oa)
     for l in range(NL):
         b.step(l, L, Ks[l], Vs[l], Qs[l], Ob[l])
+    # fewer rows than the per-layer buffers hold (layer stride > T rows): the next step with T = 2
+    a.step_layers(L + T, Ks[:, :2], Vs[:, :2], Qs[:, :2], Oa[:, :2])
+    for l in range(NL):
+        b.step(l, L + T, Ks[l, :2], Vs[l, :2], Qs[l, :2], Ob[l, :2])
     a.sync(); b.sync()
     assert torch.equal(Oa, Ob)
     for l in range(NL):
