@@ -35,7 +35,7 @@ SPEC = "K*=5r,V*=6"
 NH, NKV, HD = 24, 4, 256
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch at this workload's shapes (ncu capture of the
 # one-layer case, profiles/attn_tc_kernel_config2_one_layer.md; a launch of the 16-layer run processes the same one layer)
-NCU_TRAFFIC_BYTES = 165.8e6
+NCU_TRAFFIC_BYTES = 164.9e6
 WORKLOAD = "config2: 16 attention layers, 101,600 positions, preset F layout K5r/V6 + q8_0 window 2048, 8 queries/step, streaming append+spill+attend"
 
 
