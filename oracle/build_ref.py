@@ -4,7 +4,7 @@ its source where it lies (nothing of it is copied into this repository's history
 oracle/ref_witness.cu into oracle/_ref/libref_witness.so. The witness runs on a GPU only; tests use it to pin the CPU oracle
 and to generate the golden vectors under tests/golden/.
 
-    python oracle/build_ref.py [reference_root]        (default /root/reference)
+    python oracle/build_ref.py [reference_root]
 """
 import os
 import re
