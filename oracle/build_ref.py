@@ -1,10 +1,15 @@
 #!/usr/bin/env python
-"""Builds the reference witness: the reference project's own KV quantizer / dequantizer device functions, cut verbatim out of
-its source where it lies (nothing of it is copied into this repository's history), compiled with the small driver
-oracle/ref_witness.cu into oracle/_ref/libref_witness.so. The witness runs on a GPU only; tests use it to pin the CPU oracle
-and to generate the golden vectors under tests/golden/.
+"""Builds the reference witnesses: the reference project's own device code for this path, cut verbatim out of its source where
+it lies (nothing of it is copied into this repository's history) and compiled with the small drivers in this directory into
+the git-ignored oracle/_ref/:
 
-    python oracle/build_ref.py [reference_root]
+    libref_witness.so       quantizer / rotation / dequantizer device functions (driver: ref_witness.cu)
+    libref_attn_witness.so  the decode-attention kernels, cut by the reference's own script bench/kvattn_gen.py
+                            (driver: ref_attn_witness.cu)
+
+The witnesses run on a GPU only; tests use them to pin the CPU oracle and to generate the golden vectors under tests/golden/.
+
+    python oracle/build_ref.py <reference_root>        (or MK_REFERENCE_ROOT=<reference_root>)
 """
 import os
 import re
@@ -14,6 +19,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAMES = ["kv_store_q8", "kv_store_q4", "fwht256", "kv_store_qn", "q8_to_f16", "q4_to_f16", "kv_hi", "qn_to_f16"]
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
 def cut(src, names):
@@ -43,26 +49,53 @@ def cut(src, names):
     return "\n".join(out) + "\n"
 
 
-def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    src_path = os.path.join(ref, "qwen38_mk.cu")
-    if not os.path.exists(src_path):
-        print("build_ref: no reference tree at %s: witness not built" % ref)
-        return 0
-    os.makedirs(OUT, exist_ok=True)
-    inc = os.path.join(OUT, "ref_cut.inc")
-    with open(inc, "w") as f:
-        f.write(cut(open(src_path, encoding="utf-8").read(), NAMES))
-    so = os.path.join(OUT, "libref_witness.so")
-    # the reference's own flags for device code: -O3 -std=c++17, default -fmad (its Makefile:3-13)
-    cmd = ["nvcc", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", "-shared", "-I", OUT,
-           "-o", so, os.path.join(HERE, "ref_witness.cu")]
+def nvcc(cmd):
     r = subprocess.run(cmd, capture_output=True, text=True)
-    os.remove(inc)  # only the binary stays (and only under the git-ignored oracle/_ref)
     if r.returncode != 0:
         print(r.stdout + r.stderr)
         raise SystemExit("build_ref: nvcc failed")
+
+
+def build_quant(ref):
+    inc = os.path.join(OUT, "ref_cut.inc")
+    with open(inc, "w") as f:
+        f.write(cut(open(os.path.join(ref, "qwen38_mk.cu"), encoding="utf-8").read(), NAMES))
+    so = os.path.join(OUT, "libref_witness.so")
+    # the reference's own flags for device code: -O3 -std=c++17, default -fmad (its Makefile:3-13)
+    try:
+        nvcc(["nvcc", "-O3", "-std=c++17"] + ARCH + ["-Xcompiler", "-fPIC", "-shared", "-I", OUT, "-o", so,
+              os.path.join(HERE, "ref_witness.cu")])
+    finally:
+        os.remove(inc)  # only the binary stays (and only under the git-ignored oracle/_ref)
     print("build_ref: built", so)
+
+
+def build_attn(ref):
+    gen = os.path.join(ref, "bench", "kvattn_gen.py")
+    if not os.path.exists(gen):
+        print("build_ref: %s is missing: attention witness not built" % gen)
+        return
+    inc = os.path.join(OUT, "ref_attn_cut.inc")
+    subprocess.run([sys.executable, gen, ref, "WORK", inc], check=True, capture_output=True)
+    so = os.path.join(OUT, "libref_attn_witness.so")
+    # the flags of the reference's own recipe for these kernels (bench/kvattn_bench.cu:5), for sm_100a
+    try:
+        nvcc(["nvcc", "-O3", "-std=c++17"] + ARCH + ["-Xptxas=-dlcm=cg", "-Xcompiler", "-fPIC", "-shared", "-I", ref, "-I",
+              os.path.join(ref, "bench", "stub"), "-I", OUT, "-o", so, os.path.join(HERE, "ref_attn_witness.cu")])
+    finally:
+        os.remove(inc)
+    print("build_ref: built", so)
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MK_REFERENCE_ROOT", "")
+    if not ref or not os.path.exists(os.path.join(ref, "qwen38_mk.cu")):
+        print("build_ref: no reference tree given (argument or MK_REFERENCE_ROOT): witnesses not built")
+        return 0
+    os.makedirs(OUT, exist_ok=True)
+    build_quant(ref)
+    if "--quant-only" not in sys.argv:
+        build_attn(ref)
     return 0
 
 

@@ -440,7 +440,8 @@ int orc_append(void * h, int layer, int pos0, int n, const uint16_t * K, const u
 // Q: fp16 [T][24][256] (post-norm, post-RoPE, unscaled); O: fp32 [T][24][256] normalised (rotated back if V is stored
 // rotated). split > 1 cuts every chunk of the reference partition into that many pieces (partition-sensitivity probe).
 // Prologue qwen38_mk.cu:2876-2883, partition :2548-2573, merge :4658-4685.
-int orc_attend(void * h, int layer, int n, int T, const uint16_t * Q, float * O, int nthreads, int split) {
+static int attend_impl(void * h, int layer, int n, int T, const uint16_t * Q, float * O, int nthreads, int split, float * out_m,
+                       float * out_l, float * out_O) {
     Cache & c = *static_cast<Cache *>(h);
     if (layer < 0 || layer >= c.layers || T < 1 || T > 8 || n < 0 || n + T > c.ctxp) { g_err = "orc_attend: out of range"; return -1; }
     const int L = n + T, R = GQ * T, ws = kv_ws(L, c.win);
@@ -484,6 +485,10 @@ int orc_attend(void * h, int layer, int n, int T, const uint16_t * Q, float * O,
     for (int i = 1; i < nt; i++) th.emplace_back(work);
     work();
     for (auto & t : th) t.join();
+    if (out_m) memcpy(out_m, pm.data(), pm.size() * sizeof(float));
+    if (out_l) memcpy(out_l, pl.data(), pl.size() * sizeof(float));
+    if (out_O) memcpy(out_O, pO.data(), pO.size() * sizeof(float));
+    if (!O) return nc;
     // merge: qwen38_mk.cu:4658-4669
     for (int hq = 0; hq < NH; hq++)
         for (int t = 0; t < T; t++) {
@@ -504,7 +509,39 @@ int orc_attend(void * h, int layer, int n, int T, const uint16_t * Q, float * O,
             if (c.rot[1][layer]) fwht256(y);
             memcpy(O + ((size_t) t * NH + hq) * HD, y, sizeof y);
         }
-    return 0;
+    return nc;
+}
+int orc_attend(void * h, int layer, int n, int T, const uint16_t * Q, float * O, int nthreads, int split) {
+    return attend_impl(h, layer, n, T, Q, O, nthreads, split, nullptr, nullptr, nullptr) < 0 ? -1 : 0;
+}
+// The same call, also giving the un-normalised split partials of the reference partition (what the reference's kernels leave in
+// apart / aml, qwen38_mk.cu:3048-3064): item = kv head * chunks + chunk, row = (head % 6) T + t; m, l: [items][6 T],
+// Op: [items][6 T][256]. O may be null (partials only). Returns the number of chunks per kv head, -1 on error.
+int orc_attend_parts(void * h, int layer, int n, int T, const uint16_t * Q, float * O, int nthreads, float * m, float * l, float * Op) {
+    return attend_impl(h, layer, n, T, Q, O, nthreads, 1, m, l, Op);
+}
+// The merge alone (qwen38_mk.cu:4658-4685) over given partials of nc chunks per kv head in the layout above: O fp32 [T][24][256]
+void orc_merge_parts(int T, int nc, int rot_v, const float * pm, const float * pl, const float * pO, float * O) {
+    const int R = GQ * T;
+    for (int hq = 0; hq < NH; hq++)
+        for (int t = 0; t < T; t++) {
+            const int g = hq / GQ, r = (hq % GQ) * T + t;
+            float M = -INFINITY;
+            for (int k = 0; k < nc; k++) M = std::fmax(M, pm[((size_t) g * nc + k) * R + r]);
+            float y[HD], den = 0.f;
+            for (int d = 0; d < HD; d++) y[d] = 0.f;
+            for (int k = 0; k < nc; k++) {
+                const size_t it = (size_t) g * nc + k;
+                const float mk = pm[it * R + r];
+                const float wgt = mk == -INFINITY ? 0.f : expf(mk - M);
+                const float * o = pO + (it * R + r) * HD;
+                for (int d = 0; d < HD; d++) y[d] += wgt * o[d];
+                den += wgt * pl[it * R + r];
+            }
+            for (int d = 0; d < HD; d++) y[d] = y[d] / den;
+            if (rot_v) fwht256(y);
+            memcpy(O + ((size_t) t * NH + hq) * HD, y, sizeof y);
+        }
 }
 
 // ring rows of positions [p0, p1) rebuilt from the main rows: qwen38_mk.cu:2488-2518
@@ -538,6 +575,21 @@ int orc_ring_rewind(void * h, int P) {
     return done;
 }
 int orc_kv_top(void * h) { return static_cast<Cache *>(h)->kv_top; }
+
+// The layer's buffers where they lie (the reference layout, mk_shared.cuh:385-403): kind 0 main values [4][ctxp][32 bits], 1 main
+// scales [4][ctxp][8], 2 ring values [4][rc][256], 3 ring scales [4][rc][8] (null for a side without a ring). bytes: the size.
+void * orc_buffer(void * h, int layer, int w, int kind, long long * bytes) {
+    Cache & c = *static_cast<Cache *>(h);
+    if (layer < 0 || layer >= c.layers || w < 0 || w > 1) return nullptr;
+    switch (kind) {
+    case 0: *bytes = (long long) c.val[w][layer].size(); return c.val[w][layer].data();
+    case 1: *bytes = (long long) c.sc[w][layer].size() * 2; return c.sc[w][layer].data();
+    case 2: *bytes = (long long) c.rval[w][layer].size(); return c.has_ring[w][layer] ? c.rval[w][layer].data() : nullptr;
+    case 3: *bytes = (long long) c.rsc[w][layer].size() * 2; return c.has_ring[w][layer] ? c.rsc[w][layer].data() : nullptr;
+    }
+    return nullptr;
+}
+int orc_ctxp(void * h) { return static_cast<Cache *>(h)->ctxp; }
 
 // one row's bytes: ring = 0 main row of position pos, ring = 1 the ring row of slot index pos. val: row bytes, sc: 8 halves
 int orc_row(void * h, int layer, int w, int g, int pos, int ring, uint8_t * val, uint16_t * sc) {

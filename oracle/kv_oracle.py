@@ -41,6 +41,12 @@ def lib():
         L.orc_has_ring.argtypes = [vp, ip, ip]
         L.orc_append.argtypes = [vp, ip, ip, ip, vp, vp]
         L.orc_attend.argtypes = [vp, ip, ip, ip, vp, vp, ip, ip]
+        L.orc_attend_parts.argtypes = [vp, ip, ip, ip, vp, vp, ip, vp, vp, vp]
+        L.orc_merge_parts.restype = None
+        L.orc_merge_parts.argtypes = [ip, ip, ip, vp, vp, vp, vp]
+        L.orc_buffer.restype = vp
+        L.orc_buffer.argtypes = [vp, ip, ip, ip, vp]
+        L.orc_ctxp.argtypes = [vp]
         L.orc_refill.argtypes = [vp, ip, ip]
         L.orc_ring_rewind.argtypes = [vp, ip]
         L.orc_row.argtypes = [vp, ip, ip, ip, ip, ip, vp, vp]
@@ -122,6 +128,17 @@ def parse_spec(spec, layers):
     return kvb, rot
 
 
+def merge_parts(T, m, l, Op, rot_v=False):
+    """the reference's merge of split partials (layout of Cache.attend_parts) -> O fp32 [T][24][256]"""
+    m = np.ascontiguousarray(m, dtype=np.float32)
+    l = np.ascontiguousarray(l, dtype=np.float32)
+    Op = np.ascontiguousarray(Op, dtype=np.float32)
+    nc = m.shape[0] // NKV
+    O = np.zeros((T, NH, HD), dtype=np.float32)
+    lib().orc_merge_parts(T, nc, int(rot_v), _p(m), _p(l), _p(Op), _p(O))
+    return O
+
+
 class Cache:
     """The reference cache state (every row in its main format + the q8 rings), held in host memory."""
 
@@ -165,6 +182,35 @@ class Cache:
         if lib().orc_attend(self.h, layer, n, T, _p(Q), _p(O), threads, split) != 0:
             raise ValueError(err())
         return O
+
+    def attend_parts(self, layer, n, Q, threads=8, want_O=True):
+        """(O or None, m [items][6T], l [items][6T], Op [items][6T][256], chunks per kv head): the reference partition's split
+        partials, item = kv head * chunks + chunk, row = (head % 6) T + t"""
+        Q = np.ascontiguousarray(Q, dtype=np.float16)
+        T = Q.shape[0]
+        nch, _ = attn_dims(n + T)
+        R = 6 * T
+        m = np.zeros((NKV * nch, R), dtype=np.float32)
+        l = np.zeros((NKV * nch, R), dtype=np.float32)
+        Op = np.zeros((NKV * nch, R, HD), dtype=np.float32)
+        O = np.zeros((T, NH, HD), dtype=np.float32) if want_O else None
+        nc = lib().orc_attend_parts(self.h, layer, n, T, _p(Q), _p(O) if want_O else None, threads, _p(m), _p(l), _p(Op))
+        if nc < 0:
+            raise ValueError(err())
+        assert nc == nch
+        return O, m, l, Op, nc
+
+    def buffer(self, layer, w, kind):
+        """numpy view (uint8) of one of the layer's buffers: kind 0 main values, 1 main scales, 2 ring values, 3 ring scales"""
+        nb = C.c_longlong()
+        ptr = lib().orc_buffer(self.h, layer, w, kind, C.byref(nb))
+        if not ptr:
+            return None
+        return np.ctypeslib.as_array((C.c_uint8 * nb.value).from_address(ptr))
+
+    @property
+    def ctxp(self):
+        return lib().orc_ctxp(self.h)
 
     def refill(self, p0, p1):
         if lib().orc_refill(self.h, p0, p1) != 0:

@@ -7,10 +7,13 @@
 //   - one producer thread streams the packed K / V rows of the CTA's groups into a ring of shared-memory slots with bulk
 //     copies completing on mbarriers;
 //   - 16 unpack warps turn packed rows into exact fp16(d * q) operands in the canonical no-swizzle UMMA layouts (one thread:
-//     one position x 32 dims per step) -- K as the K-major A operand of S^T[128 pos x 48 rows] = K Q^T, V as the MN-major A
-//     operand of O^T[256 dims x 48 rows] += V^T P^T;
+//     one position x 32 dims per step; the fp16 pairs are assembled straight from the nibble words and high-bit fields with one
+//     AND-OR each, kv_unpack.h, which leaves the 8 dims of a 16-byte unit in the order UNIT_PERM: the queries are staged in the
+//     same order and the output dims are mapped back) -- K as the K-major A operand of S^T[128 pos x 48 rows] = K Q^T, V as the
+//     MN-major A operand of O^T[256 dims x 48 rows] += V^T P^T;
 //   - one issuer thread runs tcgen05.mma on the slots as they fill (mbarrier "full" from the unpack warps, tcgen05.commit
-//     to "empty"), S^T triple-buffered in tensor memory, O^T (two 128-dim halves) resident there for the whole kernel;
+//     to "empty"), S^T in five tensor-memory buffers (K runs five groups ahead of V), O^T (two 128-dim halves) resident there
+//     for the whole kernel;
 //   - 8 softmax warps read S^T back (tcgen05.ld: a thread owns one position and 24 query rows), take the tile maxima,
 //     exchange the running max with the CTAs that hold the chunk's earlier groups through small global arrays (own group
 //     maxima and cumulative maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as
@@ -22,8 +25,9 @@
 //     bounded wait) each merges one or two of the head's rows in the kernel's tail (merge_row);
 //   - batch mode (several jobs): one CTA per (job, kv head, chunk) in a plain launch, the chunk's groups in order on that CTA with
 //     the running max carried in registers; attn_merge_kernel afterwards.
-// Every wait is bounded (about two seconds), then the status word is set and the kernel runs to its end and frees its
-// tensor memory.
+// Every wait is bounded (about two seconds by default; the limits are launch arguments), then the status word and a CTA-wide
+// flag are set, no later wait of the CTA blocks, the producer waits (bounded) for its copies still in flight, and the kernel
+// runs to its end and frees its tensor memory.
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -66,13 +70,19 @@ constexpr int RAW_SLOT = ATP * HD + ATP * SCALE_ROW; // one tile of the widest f
 constexpr int NRAW = 9;
 constexpr int OP_SLOT = GP * 128 * 2;       // fp16 operand: 128 positions x 128 dims
 constexpr int NOP = 3;
-constexpr int NSB = 3;                      // S^T buffers
+constexpr int NSB = 5;                      // S^T buffers: K runs NSB groups ahead of V
 constexpr int Q_BYTES = AR * HD * 2, P_BYTES = AR * GP * 2;
-constexpr unsigned S_COL = 0, S_STRIDE = 64, O_COL0 = 192, O_COL1 = 320, TMEM_COLS = 512; // an O^T half: 48 columns for P's high part, 48 for its low part
+constexpr unsigned S_COL = 0, S_STRIDE = 64, O_COL0 = NSB * 64, O_COL1 = O_COL0 + 2 * AR, TMEM_COLS = 512; // an O^T half: 48 columns for P's high part, 48 for its low part
+static_assert(O_COL1 + 2 * AR <= TMEM_COLS, "tensor-memory columns");
 // The accumulator's reference max of a row is set REF_MARGIN above the running max it is taken from and moves when the running max
 // passes it by more than REF_SLACK: exp(running - reference) stays within [e^-3 for the row's largest terms, e^10.5 < fp16 max].
 constexpr float REF_SLACK = 10.5f, REF_MARGIN = 3.f;
 constexpr float LOG2E = 1.4426950408889634f;
+
+struct WaitCtl { // the launch's wait limits and the CTA's give-up flag
+    int dead;
+    unsigned hint, rounds, poll; // nanoseconds per failed try, failed tries of an mbarrier wait, failed polls of a global word
+};
 
 struct WarpScratch { // what the row-owner lanes of a softmax warp hand to all its lanes
     float m[RS];     // running max of the warp's tile (+inf where nothing is visible yet: exp2 gives 0)
@@ -86,13 +96,13 @@ struct Smem {
     uint8_t raw[NRAW][RAW_SLOT];
     uint8_t q[Q_BYTES];         // [dim group 32][row group 6][8 rows][8 dims]
     uint8_t p[2][P_BYTES];      // high / low part: [row group 6][position group 16][8 positions][8 rows]
-    int tmax[3][GT][AR];        // row maxima of a group's tiles as order-preserving integer keys; by group % 3: a group's maxima are
-                                // read while the next group's are written, and a warp is never two groups ahead of its slice.
+    float tmax[3][GT][AR];      // row maxima of a group's tiles; by group % 3: a group's maxima are read while the next group's
+                                // are written, and a warp is never two groups ahead of its slice.
                                 // The first buffer holds the row sums at the end.
     WarpScratch ws[NSOFT];
     unsigned char rtok[AR];     // token of a query row
     unsigned tmem_base;
-    int dead;                   // a wait of this CTA gave up: no later wait blocks
+    WaitCtl wc;                 // the launch's wait limits; dead: a wait of this CTA gave up, no later wait blocks
     AttnTask tasks[8];          // the CTA's groups as the producer reaches them, by group % 8 (no role is 8 groups apart from it)
     uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[NSB], s_empty[NSB], p_full, p_empty;
     AttnJob job;
@@ -114,6 +124,8 @@ struct Args {
     unsigned done_target;   // the count that means "every CTA of the head, this launch"; done == null: separate merge launch
     unsigned long long * prof; // optional: [CTA][16 groups][20] globaltimer stamps: softmax warp 0 (0 .. 7), unpack warp 8 (8 .. 15),
                                // issuer (16 .. 19)
+    unsigned wait_hint_ns, wait_rounds, poll_rounds; // limits of the waits: a failed mbarrier try suspends for up to wait_hint_ns,
+                                                     // wait_rounds failed tries (poll_rounds failed polls of an exchange word) give up
 };
 #ifndef MKKV_TC_PROF
 #define MKKV_TC_PROF 0 // 1: compile the phase stamps in (they cost a few per cent)
@@ -131,28 +143,27 @@ struct Args {
 #endif
 
 // Wait for a phase of an mbarrier. A failed try suspends the thread in hardware for up to the hinted time (it wakes when the phase
-// completes), so waiting warps take next to no issue slots. Bounded: after WAIT_ROUNDS failed tries the status word and the CTA's
+// completes), so waiting warps take next to no issue slots. Bounded: after `rounds` failed tries the status word and the CTA's
 // `dead` flag are set; from then on no wait of this CTA blocks, and the kernel runs to its end.
-#ifndef MKKV_WAIT_HINT_NS
-#define MKKV_WAIT_HINT_NS 10000
-#endif
-constexpr unsigned WAIT_HINT_NS = MKKV_WAIT_HINT_NS, WAIT_ROUNDS = 200000u;
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t * bar, unsigned parity) {
+constexpr unsigned WAIT_HINT_NS = 10000u, WAIT_ROUNDS = 200000u, POLL_ROUNDS = 1u << 21; // defaults: about two seconds each
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t * bar, unsigned parity, unsigned hint_ns) {
     unsigned ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void tc_wait(uint64_t * bar, unsigned parity, volatile int * dead, int * status) {
-    for (unsigned it = 0; !mbar_try_wait_hint(bar, parity); it++) {
-        if (*dead) return;
-        if (it >= WAIT_ROUNDS) {
-            *dead = 1;
+__device__ __forceinline__ void tc_wait(uint64_t * bar, unsigned parity, volatile WaitCtl * wc, int * status) {
+    if (mbar_try_wait_hint(bar, parity, 0u)) return; // (the common case: no limit loaded)
+    const unsigned hint = wc->hint, rounds = wc->rounds;
+    for (unsigned it = 0; !mbar_try_wait_hint(bar, parity, hint); it++) {
+        if (wc->dead) return;
+        if (it >= rounds) {
+            wc->dead = 1;
             atomicExch(status, (int) KS_WAIT_TIMEOUT);
             return;
         }
@@ -233,54 +244,77 @@ __device__ __forceinline__ float exp_neg(float x) {
 }
 
 // ---- one worker step: position `row` of a staged tile, dims 32 jb .. 32 jb + 31 -> four 16-byte operand units ----
-// FMT 0 .. 3: rows of 4 + FMT bits; FMT 4: q8_0 rows. dst: the thread's unit of dim group 4 (jb & 3) of the slot; the next
-// dim groups are 2048 bytes apart. valid false (a row past the chunk end holds stale bytes): zeros.
-template <int FMT> __device__ __forceinline__ void dq_item(const uint8_t * raw, int row, int jb, bool valid, uint8_t * dst) {
-    constexpr int HB = FMT < 4 ? FMT : 0;
-    constexpr int RB = FMT < 4 ? 32 * (4 + FMT) : HD;
-    const __half2 sub = __half2half2(__float2half_rn(FMT < 4 ? 1024.f + (float) (1 << (3 + FMT)) : 1152.f));
+// A unit holds the 8 values of one lane word in the order UNIT_PERM (kv_unpack.h). dst: the thread's unit of dim group 4 (jb & 3)
+// of the slot; the next dim groups are 2048 bytes apart. valid false (a row past the chunk end holds stale bytes): zeros.
+// fp16(d * q) of a pair held as (bias + n): the difference is exact, the product is rounded once
+__device__ __forceinline__ unsigned pair_val(unsigned x, unsigned sub, __half2 d) {
+    const __half2 h = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&x), *reinterpret_cast<const __half2 *>(&sub)), d);
+    return *reinterpret_cast<const unsigned *>(&h);
+}
+template <int BITS> __device__ __forceinline__ void store_unit(uint8_t * dst, const unsigned (&x)[4], __half2 d) {
+    const unsigned sa = pair_sub_a<BITS>(), sb = BITS >= 7 ? sa : pair_sub_b<BITS>();
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(pair_val(x[0], sa, d), pair_val(x[1], sb, d), pair_val(x[2], sa, d), pair_val(x[3], sb, d));
+}
+template <int BITS> __device__ __forceinline__ void dq_item(const uint8_t * raw, int row, int jb, bool valid, uint8_t * dst) {
     const __half dsc = valid ? reinterpret_cast<const __half *>(raw + TILE_SC_OFF)[row * 8 + jb] : __float2half_rn(0.f);
     const __half2 d = __half2half2(dsc);
-    const uint8_t * rp = raw + row * RB;
-    if constexpr (FMT == 4) {
+    const uint8_t * rp = raw + row * (32 * BITS);
+    unsigned x[4];
+    if constexpr (BITS == 8) {
         const uint4 v0 = *reinterpret_cast<const uint4 *>(rp + 32 * jb), v1 = *reinterpret_cast<const uint4 *>(rp + 32 * jb + 16);
         const unsigned w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            const unsigned x0 = w[2 * u] ^ 0x80808080u, x1 = w[2 * u + 1] ^ 0x80808080u; // q + 128
-            *reinterpret_cast<uint4 *>(dst + u * 2048) =
-                make_uint4(cvt_pair<0>(x0, sub, d), cvt_pair<1>(x0, sub, d), cvt_pair<0>(x1, sub, d), cvt_pair<1>(x1, sub, d));
+            const unsigned lo = w[2 * u] ^ 0x80808080u, hi = w[2 * u + 1] ^ 0x80808080u; // q + 128
+            x[0] = __byte_perm(lo, MAGIC_A, 0x7270); // (value 0, value 2) under the exponent of 1024
+            x[1] = __byte_perm(hi, MAGIC_A, 0x7270); // (4, 6)
+            x[2] = __byte_perm(lo, MAGIC_A, 0x7371); // (1, 3)
+            x[3] = __byte_perm(hi, MAGIC_A, 0x7371); // (5, 7)
+            store_unit<8>(dst + u * 2048, x, d);
         }
     } else {
         const uint4 nv = *reinterpret_cast<const uint4 *>(rp + 16 * jb);
         const unsigned nw[4] = {nv.x, nv.y, nv.z, nv.w};
-        unsigned hw[4] = {0u, 0u, 0u, 0u};
-        if constexpr (HB == 1) {
+        if constexpr (BITS == 4) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                pair_words<4>(nw[u], 0u, x);
+                store_unit<4>(dst + u * 2048, x, d);
+            }
+        } else if constexpr (BITS == 5) {
             const unsigned h = *reinterpret_cast<const unsigned *>(rp + 128 + 4 * jb);
-            hw[0] = h, hw[1] = h >> 8, hw[2] = h >> 16, hw[3] = h >> 24;
-        } else if constexpr (HB == 2) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                pair_words<5>(nw[u], __byte_perm(h, 0u, 0x4440 + u), x);
+                store_unit<5>(dst + u * 2048, x, d);
+            }
+        } else if constexpr (BITS == 6) {
             const uint2 h = *reinterpret_cast<const uint2 *>(rp + 128 + 8 * jb);
-            hw[0] = h.x, hw[1] = h.x >> 16, hw[2] = h.y, hw[3] = h.y >> 16;
-        } else if constexpr (HB == 3) {
+            const unsigned hw[4] = {h.x, h.x >> 16, h.y, h.y >> 16}; // (pair_words masks the fields it reads)
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                pair_words<6>(nw[u], hw[u], x);
+                store_unit<6>(dst + u * 2048, x, d);
+            }
+        } else {
             const unsigned * hp = reinterpret_cast<const unsigned *>(rp + 128 + 12 * jb);
             const unsigned h0 = hp[0], h1 = hp[1], h2 = hp[2];
-            hw[0] = h0, hw[1] = __funnelshift_r(h0, h1, 24), hw[2] = __funnelshift_r(h1, h2, 16), hw[3] = h2 >> 8;
-        }
+            const unsigned hw[4] = {h0, __funnelshift_r(h0, h1, 24), __funnelshift_r(h1, h2, 16), h2 >> 8}; // (bits above 23: not read)
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const unsigned x0 = quad_bytes<HB>(nw[u], hw[u], 0), x1 = quad_bytes<HB>(nw[u], hw[u], 1);
-            *reinterpret_cast<uint4 *>(dst + u * 2048) =
-                make_uint4(cvt_pair<0>(x0, sub, d), cvt_pair<1>(x0, sub, d), cvt_pair<0>(x1, sub, d), cvt_pair<1>(x1, sub, d));
+            for (int u = 0; u < 4; u++) {
+                pair_words7(nw[u], hw[u], x);
+                store_unit<7>(dst + u * 2048, x, d);
+            }
         }
     }
 }
 __device__ __forceinline__ void dq_item_any(int bits, const uint8_t * raw, int row, int jb, bool valid, uint8_t * dst) {
     switch (bits) {
-    case 4: dq_item<0>(raw, row, jb, valid, dst); break;
-    case 5: dq_item<1>(raw, row, jb, valid, dst); break;
-    case 6: dq_item<2>(raw, row, jb, valid, dst); break;
-    case 7: dq_item<3>(raw, row, jb, valid, dst); break;
-    default: dq_item<4>(raw, row, jb, valid, dst); break;
+    case 4: dq_item<4>(raw, row, jb, valid, dst); break;
+    case 5: dq_item<5>(raw, row, jb, valid, dst); break;
+    case 6: dq_item<6>(raw, row, jb, valid, dst); break;
+    case 7: dq_item<7>(raw, row, jb, valid, dst); break;
+    default: dq_item<8>(raw, row, jb, valid, dst); break;
     }
 }
 
@@ -292,13 +326,18 @@ __device__ __forceinline__ int f2key(float x) {
 __device__ __forceinline__ float key2f(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 
 // bounded poll of an exchange word until it carries this launch's tag
-__device__ __forceinline__ float poll_word(const unsigned long long * src, unsigned long long w, int epoch, int * status) {
-    for (unsigned it = 0; (unsigned) (w >> 32) != (unsigned) epoch; it++) {
-        if (it >= (1u << 21)) { // (a round is a trip to the L2: seconds)
-            atomicExch(status, (int) KS_WAIT_TIMEOUT);
-            break;
+__device__ __forceinline__ float poll_word(const unsigned long long * src, unsigned long long w, int epoch, volatile WaitCtl * wc, int * status) {
+    if ((unsigned) (w >> 32) != (unsigned) epoch) {
+        const unsigned rounds = wc->poll;
+        for (unsigned it = 0; (unsigned) (w >> 32) != (unsigned) epoch; it++) {
+            if (wc->dead) break;
+            if (it >= rounds) { // (a round is a trip to the L2)
+                wc->dead = 1;
+                atomicExch(status, (int) KS_WAIT_TIMEOUT);
+                break;
+            }
+            w = __ldcv(src);
         }
-        w = __ldcv(src);
     }
     return __uint_as_float((unsigned) w);
 }
@@ -349,7 +388,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         for (int s = 0; s < NSB; s++) { mbar_init(&sm.s_full[s], 1); mbar_init(&sm.s_empty[s], NSOFT); }
         mbar_init(&sm.p_full, NSOFT);
         mbar_init(&sm.p_empty, 1);
-        sm.dead = 0;
+        sm.wc.dead = 0;
+        sm.wc.hint = a.wait_hint_ns;
+        sm.wc.rounds = a.wait_rounds;
+        sm.wc.poll = a.poll_rounds;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == W_ISSUE) { // tensor memory: S^T three times, O^T in two halves
@@ -424,7 +466,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 for (int qq = 0; qq < GT; qq++, rseq++) {
                     const int rs = rseq % NRAW;
                     const unsigned round = rseq / NRAW;
-                    if (round > 0) tc_wait(&sm.raw_empty[rs], (round - 1) & 1, &sm.dead, a.status);
+                    if (round > 0) tc_wait(&sm.raw_empty[rs], (round - 1) & 1, &sm.wc, a.status);
                     if (qq < k.nt) issue_tile(S, k.pos0 + qq * ATP, k.c1, sm.raw[rs], &sm.raw_full[rs]);
                     else mbar_arrive(&sm.raw_full[rs]);
                 }
@@ -442,12 +484,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 const bool isK = nk < G && nk < nv + NSB;
                 if (isK) { // S^T(nk) = K Q^T
                     const int sb = nk % NSB;
-                    if (nk >= NSB) tc_wait(&sm.s_empty[sb], ((nk / NSB) - 1) & 1, &sm.dead, a.status);
+                    if (nk >= NSB) tc_wait(&sm.s_empty[sb], ((nk / NSB) - 1) & 1, &sm.wc, a.status);
                     const unsigned dcol = tb + S_COL + S_STRIDE * sb;
 #pragma unroll 1
                     for (int h = 0; h < 2; h++, oseq++) {
                         const int os = oseq % NOP;
-                        tc_wait(&sm.op_full[os], (oseq / NOP) & 1, &sm.dead, a.status);
+                        tc_wait(&sm.op_full[os], (oseq / NOP) & 1, &sm.wc, a.status);
                         tc_fence_after();
                         const unsigned a_lo = desc_lo(smem_u32(sm.op[os]), 2048), b_lo = q_lo + ((8 * h) * (2 * AR / 8 * 128) >> 4);
 #pragma unroll
@@ -459,12 +501,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     nk++;
                 } else { // O^T += V^T P^T(nv), P as its high and low parts
                     TC_STAMP(nv, 16);
-                    tc_wait(&sm.p_full, nv & 1, &sm.dead, a.status);
+                    tc_wait(&sm.p_full, nv & 1, &sm.wc, a.status);
                     TC_STAMP(nv, 17);
 #pragma unroll 1
                     for (int h = 0; h < 2; h++, oseq++) {
                         const int os = oseq % NOP;
-                        tc_wait(&sm.op_full[os], (oseq / NOP) & 1, &sm.dead, a.status);
+                        tc_wait(&sm.op_full[os], (oseq / NOP) & 1, &sm.wc, a.status);
                         if (h == 0) TC_STAMP(nv, 18);
                         tc_fence_after();
                         const unsigned a_lo = desc_lo(smem_u32(sm.op[os]), 128), dcol = tb + (h ? O_COL1 : O_COL0);
@@ -493,7 +535,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             const int side = isK ? 0 : 1, grp = isK ? nk - NSB : nv;
             (void) grp; // (the stamps' group index)
             if (st) TC_STAMP(grp, side ? 8 : 11);
-            tc_wait(&sm.raw_full[rs], rph, &sm.dead, a.status);
+            tc_wait(&sm.raw_full[rs], rph, &sm.wc, a.status);
             if (st) TC_STAMP(grp, side ? 9 : 12);
             const AttnTask & kr = sm.tasks[(isK ? nk : nv) & 7];
             const int k_pos0 = kr.pos0;
@@ -507,7 +549,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             const int jr = (c + (lane >> (bits == 6 ? 1 : (bits == 5 || bits == 7) ? 2 : 0))) & 3;
 #pragma unroll 1
             for (int h = 0; h < 2; h++) {
-                if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.dead, a.status);
+                if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.wc, a.status);
                 dq_item_any(bits, sm.raw[rs], lane, 4 * h + jr, valid, sm.op[os] + 4 * jr * 2048 + pos_off);
                 fence_async_smem();
                 __syncwarp();
@@ -567,7 +609,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         // tile maxima of group j, its own maxima published, the words its running max will need requested
         auto maxima = [&](int j) {
             if (st) TC_STAMP(j, 0);
-            tc_wait(&sm.s_full[j % NSB], (j / NSB) & 1, &sm.dead, a.status);
+            tc_wait(&sm.s_full[j % NSB], (j / NSB) & 1, &sm.wc, a.status);
             const Task k = sm.tasks[j & 7];
             if (st) TC_STAMP(j, 1);
             tc_fence_after();
@@ -614,9 +656,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 float m_in = batch && k.b > 0 ? carry : -CUDART_INF_F;
                 const size_t xb0 = xbase(k);
                 if (!batch && k.nb > 1) {
-                    if (k.b >= 1) m_in = poll_word(a.xa + xb0 + (size_t) (k.b - 1) * AR, w1, a.epoch, a.status);
-                    if (k.b >= 2) m_in = fmaxf(m_in, poll_word(a.xa + xb0 + (size_t) (k.b - 2) * AR, w2, a.epoch, a.status));
-                    if (k.b >= 3) m_in = fmaxf(m_in, poll_word(a.xb + xb0 + (size_t) (k.b - 3) * AR, w0, a.epoch, a.status));
+                    if (k.b >= 1) m_in = poll_word(a.xa + xb0 + (size_t) (k.b - 1) * AR, w1, a.epoch, &sm.wc, a.status);
+                    if (k.b >= 2) m_in = fmaxf(m_in, poll_word(a.xa + xb0 + (size_t) (k.b - 2) * AR, w2, a.epoch, &sm.wc, a.status));
+                    if (k.b >= 3) m_in = fmaxf(m_in, poll_word(a.xb + xb0 + (size_t) (k.b - 3) * AR, w0, a.epoch, &sm.wc, a.status));
                 }
                 if (st) TC_STAMP(i, 7);
                 const int(&tm)[GT][AR] = sm.tmax[i % 3];
@@ -655,7 +697,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             const unsigned anyf = __ballot_sync(FULL_MASK, owner && f != 1.f);
             __syncwarp();
             if (st) TC_STAMP(i, 4);
-            if (i > 0) tc_wait(&sm.p_empty, (i - 1) & 1, &sm.dead, a.status); // P V of the previous group is complete: P is free, O^T at rest
+            if (i > 0) tc_wait(&sm.p_empty, (i - 1) & 1, &sm.wc, a.status); // P V of the previous group is complete: P is free, O^T at rest
             if (st) TC_STAMP(i, 5);
             tc_fence_after();
 #if MKKV_TC_PROF
@@ -742,7 +784,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     request_words(kn);
                 }
             }
-            tc_wait(&sm.p_empty, (G - 1) & 1, &sm.dead, a.status);
+            tc_wait(&sm.p_empty, (G - 1) & 1, &sm.wc, a.status);
             tc_fence_after();
         }
         // ---- the CTA's partial: O^T lanes are dims, columns are query rows ----
@@ -790,7 +832,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     unsigned it = 0;
                     while ((int) (ld_acquire_u32(a.done + g) - a.done_target) < 0) {
                         __nanosleep(100);
-                        if (++it >= (1u << 23) || sm.dead) { // (about a second)
+                        if (++it >= (sm.wc.poll << 2) || sm.wc.dead) { // (about a second)
                             atomicExch(a.status, (int) KS_WAIT_TIMEOUT);
                             ok = false;
                             break;

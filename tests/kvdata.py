@@ -57,3 +57,43 @@ def edge_rows():
     for _ in range(7):
         rows.append((rng.standard_normal(HD) * rng.uniform(0.01, 50)).astype(np.float16).astype(np.float32))
     return np.stack(rows).astype(np.float32)
+
+
+def unit_multiset():
+    """256 values on the 1/16 grid, shaped like N(0,1) quantiles, whose squares sum to exactly 256 (mean square exactly 1).
+    Every partial sum of their squares is exact in fp32, so an RMS-norm of a row made of them sees exactly 1.0 in any
+    summation order: the rows of the attention fixtures pass the reference kernels' norm prologue unchanged."""
+    from statistics import NormalDist
+    nd = NormalDist()
+    a = np.array([round(16 * nd.inv_cdf((i + 0.5) / 256)) for i in range(256)], dtype=np.int64)
+    target = 256 * 256
+    # move single values by one grid step, largest magnitudes first, until the sum of squares is hit
+    order = np.argsort(-np.abs(a))
+    for _ in range(10000):
+        s = int((a * a).sum())
+        if s == target:
+            break
+        moved = False
+        for i in order:
+            step = 1 if s < target else -1
+            b = abs(int(a[i])) + step
+            delta = b * b - int(a[i]) ** 2
+            if b >= 1 and ((s < target and s + delta <= target) or (s > target and s + delta >= target)):
+                a[i] = b if a[i] >= 0 else -b
+                moved = True
+                break
+        if not moved:  # the remaining gap is smaller than any single step of a large value: use the small ones
+            order = np.argsort(np.abs(a))
+    assert int((a * a).sum()) == target and np.abs(a).max() < 128
+    return (a / 16.0).astype(np.float32)
+
+
+def unit_rows(seed, tag, shape_prefix):
+    """fp16 rows [*shape_prefix][256]: each a random signed permutation of unit_multiset()"""
+    base = unit_multiset()
+    rng = np.random.default_rng([seed, tag, 17])
+    n = int(np.prod(shape_prefix))
+    out = np.empty((n, HD), dtype=np.float32)
+    for i in range(n):
+        out[i] = base[rng.permutation(HD)] * rng.choice(np.array([-1.0, 1.0], dtype=np.float32), size=HD)
+    return out.reshape(*shape_prefix, HD).astype(np.float16)
