@@ -47,8 +47,17 @@ void mk_free(void * h);
 void mk_reset(void * h);
 /* All later launches go to this cudaStream_t (default: the legacy default stream, as the reference: engine_impl.h:327) */
 int mk_kv_set_stream(void * h, void * cuda_stream);
-/* Waits for the engine's streams; -1 if a kernel reported a wait that ran out (the engine is reset) */
+/* Waits for the engine's streams; -1 if a kernel reported a wait that ran out (the engine is reset), the reference's error-word
+ * convention (mk_shared.cuh:170-203, capi.cpp:219-244) */
 int mk_kv_sync(void * h);
+/* Every device-side wait of the decode-attention kernel is bounded: a failed try of a shared-memory barrier suspends the thread for
+ * up to hint_ns, after `rounds` failed tries (or `polls` failed reads of another CTA's exchange word) the CTA gives up: it sets the
+ * status word mk_kv_sync reports, stops waiting, lets its copies in flight land, frees its tensor memory and returns. These calls
+ * set the limits for the launches that follow, process-wide (defaults: 10,000 ns, 200,000, 2,097,152: about two seconds;
+ * (0, 0, 0) restores them). mk_kv_wait_limits_expire_now makes the first wait that does not succeed at once give up: the
+ * failure-path test uses it (nothing traps or hangs: the kernel returns with a wrong result the host rejects). */
+int mk_kv_wait_limits(unsigned hint_ns, unsigned rounds, unsigned polls);
+int mk_kv_wait_limits_expire_now(void);
 
 /* ---- the hot path ---- */
 /* The reference's K / V row jobs (qwen38_mk.cu:2892-2926) and pk_attn_prep's store part (prefill.cuh:984-1023):
@@ -65,8 +74,8 @@ int mk_kv_attend(void * h, int seq, int layer, int n, int T, const void * Q, voi
  * Same arguments, same result. The split-K partials go to a fixed array compiled into the library (3.96 MB on every GPU
  * that loads it, until the process exits) instead of the engine's allocated workspace; the call runs no cudaMalloc /
  * cudaFree or any other allocating routine. Limits: one sequence per call, T <= 8, at most 80 (kv head, chunk) items; a call
- * beyond that returns -1 with a message saying so. The first call on a device looks up the array's device address: make
- * that first call before any stream capture. All handles of a process share the one array per GPU, and it keeps the last
+ * beyond that returns -1 with a message saying so. The array's device address is looked up when an engine is created on the device
+ * (mk_kv_new), not in this call. All handles of a process share the one array per GPU, and it keeps the last
  * call's contents (nothing in it needs clearing: each call writes every partial it reads): two such calls that can
  * overlap on the GPU (different streams or handles) race and must be serialised by the caller. 0 / -1 */
 int mk_kv_attend_static(void * h, int seq, int layer, int n, int T, const void * Q, void * O);
@@ -111,13 +120,16 @@ int mk_checkpoints(void * h, int * out, int cap);
 int mk_kv_checkpoints(void * h, int seq, int * out, int cap);
 /* capi.cpp:600-603: 0, or -1 (no checkpoint there) */
 int mk_rewind_to(void * h, int pos);
+/* capi.cpp:590-592: to the last checkpoint; 0, or -1 (none) */
+int mk_rewind_to_checkpoint(void * h);
 int mk_kv_rewind_to(void * h, int seq, int pos);
 
 /* ---- conversation state in pinned host memory (capi.cpp:644-741) ---- */
 int mk_store_budget(void * h, long long bytes);
 int mk_store_reserve(void * h, long long bytes);
-/* out[0..9]: budget, allocated, used bytes, parked entries, last copy's bytes and microseconds, side request's copy-out
- * microseconds, bytes per KV token, 0, 0 */
+/* capi.cpp:659-673. out[0..9]: budget, allocated, used bytes, parked entries, last copy's bytes and microseconds, side request's
+ * copy-out microseconds, bytes per KV token, the last mk_side_end_park's park of the side request's conversation: bytes and
+ * microseconds */
 int mk_store_info(void * h, long long * out, int cap);
 void mk_kv_sizes(void * h, long long * per_token, long long * rings, long long * state, long long * checkpoint);
 /* id > 0, 0 (empty sequence), -3 (no room in the store), -1 error */
@@ -138,11 +150,19 @@ int mk_kv_store_wait(void * h);
 /* capi.cpp:683-711 */
 int mk_side_begin(void * h);
 int mk_side_end(void * h);
+/* capi.cpp:696-700: mk_side_end with the side request's own conversation parked first (*id: its entry, 0: not parked). 1 the kept
+ * sequence is back; 0 it was lost, the side request's conversation stays the engine's sequence; -1 error */
+int mk_side_end_park(void * h, int max_checkpoints, int * id);
+/* capi.cpp:702-707: right after mk_side_begin, the side request continues parked conversation id (the entry is freed; the kept
+ * sequence stays aside). 0 done, 1 no room in the store (nothing changed), -1 no such entry / error */
+int mk_side_unpark(void * h, int id);
 int mk_side_drop(void * h);
 int mk_side_active(void * h);
 
 /* ---- parallel slots (capi.cpp mk_slots_open; lanes.cu:291-326): n sequences of ctx positions each; returns ctx ---- */
 int mk_slots_open(void * h, int n, int ctx);
+/* capi.cpp:318-326: the same with the reference's prefill segment length, which this path (no token-level prefill) ignores */
+int mk_slots_open2(void * h, int n, int ctx, int seg_tokens);
 int mk_slots_count(void * h);
 
 /* ---- test helpers ---- */

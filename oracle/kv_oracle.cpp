@@ -418,6 +418,7 @@ void * orc_new(int layers, int ctx, const char * spec, int win, int win_all) {
 void orc_free(void * h) { delete static_cast<Cache *>(h); }
 int orc_ring_rows(void * h) { return static_cast<Cache *>(h)->rc; }
 int orc_bits(void * h, int w, int l) { return static_cast<Cache *>(h)->kvb[w][l]; }
+int orc_rot(void * h, int w, int l) { return static_cast<Cache *>(h)->rot[w][l]; }
 int orc_has_ring(void * h, int w, int l) { return static_cast<Cache *>(h)->has_ring[w][l]; }
 
 // K, V: fp16 [n][4][256] (post-norm, post-RoPE rows). Writes rows pos0 .. pos0 + n - 1 of the layer (main + ring)

@@ -38,6 +38,7 @@ def lib():
         for name in ("orc_ring_rows", "orc_kv_top"):
             getattr(L, name).argtypes = [vp]
         L.orc_bits.argtypes = [vp, ip, ip]
+        L.orc_rot.argtypes = [vp, ip, ip]
         L.orc_has_ring.argtypes = [vp, ip, ip]
         L.orc_append.argtypes = [vp, ip, ip, ip, vp, vp]
         L.orc_attend.argtypes = [vp, ip, ip, ip, vp, vp, ip, ip]
@@ -162,6 +163,9 @@ class Cache:
 
     def bits(self, w, layer):
         return lib().orc_bits(self.h, w, layer)
+
+    def rot(self, w, layer):
+        return bool(lib().orc_rot(self.h, w, layer))
 
     def has_ring(self, w, layer):
         return bool(lib().orc_has_ring(self.h, w, layer))

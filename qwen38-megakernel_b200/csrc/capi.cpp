@@ -131,6 +131,16 @@ int mk_kv_sync(void * hp) {
     });
 }
 
+int mk_kv_wait_limits(unsigned hint_ns, unsigned rounds, unsigned polls) {
+    if (hint_ns == 0 && rounds == 0 && polls == 0) mkkv::attend_tc_default_wait_limits();
+    else mkkv::attend_tc_set_wait_limits(hint_ns, rounds, polls);
+    return 0;
+}
+int mk_kv_wait_limits_expire_now(void) {
+    mkkv::attend_tc_set_wait_limits(0u, 0u, 0u);
+    return 0;
+}
+
 int mk_kv_append(void * hp, int seq, int layer, int pos0, int n, const void * K, const void * V) {
     return guarded(hp, [&](KvEngine * e) {
         e->append(seq, layer, pos0, n, K, V);
@@ -233,6 +243,9 @@ int mk_kv_rewind_to(void * hp, int seq, int pos) {
     return guarded(hp, [&](KvEngine * e) { return e->rewind_to(seq, pos) ? 0 : -1; });
 }
 int mk_rewind_to(void * hp, int pos) { return mk_kv_rewind_to(hp, MK_SEQ_MAIN, pos); }
+int mk_rewind_to_checkpoint(void * hp) {
+    return guarded(hp, [](KvEngine * e) { return e->rewind_to_checkpoint(mkkv::SEQ_MAIN) ? 0 : -1; });
+}
 
 int mk_store_budget(void * hp, long long bytes) {
     return guarded(hp, [&](KvEngine * e) {
@@ -252,7 +265,8 @@ int mk_store_info(void * hp, long long * out, int cap) {
         size_t pt, rings, state, ck;
         e->kv_sizes(&pt, &rings, &state, &ck);
         const long long v[] = {(long long) s.budget, (long long) s.allocated, (long long) s.used, s.parked, (long long) s.last_bytes,
-                               (long long) (s.last_ms * 1000.0), (long long) (s.side_ms * 1000.0), (long long) pt, 0, 0};
+                               (long long) (s.last_ms * 1000.0), (long long) (s.side_ms * 1000.0), (long long) pt,
+                               (long long) s.side_park_bytes, (long long) (s.side_park_ms * 1000.0)};
         const int n = std::min(cap, (int) (sizeof v / sizeof v[0]));
         for (int i = 0; i < n; i++) out[i] = v[i];
         return n;
@@ -322,6 +336,21 @@ int mk_side_begin(void * hp) {
 int mk_side_end(void * hp) {
     return guarded(hp, [](KvEngine * e) { return e->side_end(); });
 }
+int mk_side_end_park(void * hp, int max_checkpoints, int * id) {
+    if (!id) {
+        g_err = "mk_side_end_park: null id";
+        return -1;
+    }
+    *id = 0;
+    return guarded(hp, [&](KvEngine * e) { return e->side_end_park(max_checkpoints, id); });
+}
+int mk_side_unpark(void * hp, int id) {
+    return guarded(hp, [&](KvEngine * e) {
+        const int r = e->side_unpark(id);
+        if (r < 0) g_err = "no parked conversation " + std::to_string(id);
+        return r < 0 ? -1 : r == 1 ? 0 : 1;
+    });
+}
 int mk_side_drop(void * hp) {
     return guarded(hp, [](KvEngine * e) {
         e->side_drop();
@@ -332,6 +361,10 @@ int mk_side_active(void * hp) { return hp && static_cast<Handle *>(hp)->eng->sid
 
 int mk_slots_open(void * hp, int n, int ctx) {
     return guarded(hp, [&](KvEngine * e) { return e->slots_open(n, ctx); });
+}
+int mk_slots_open2(void * hp, int n, int ctx, int seg_tokens) {
+    (void) seg_tokens; // the reference's prefill segment length: this path has no token-level prefill
+    return mk_slots_open(hp, n, ctx);
 }
 int mk_slots_count(void * hp) {
     return guarded(hp, [](KvEngine * e) { return e->slots_count(); });

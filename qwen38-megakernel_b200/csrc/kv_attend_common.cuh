@@ -38,11 +38,19 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// bounded wait (about two seconds): on expiry the status word is set and the caller goes on, so the kernel always ends
-__device__ __forceinline__ void mbar_wait(uint64_t * bar, unsigned parity, int * status) {
-    // (a try_wait suspends the thread for a hardware-chosen time before it reports failure: 2^23 rounds are seconds)
+// Bounded wait. A failed try_wait suspends the thread for a hardware-chosen time before it reports failure, so `rounds` failed
+// tries (default 2^23) are seconds. On expiry the status word and the CTA's give-up flag are set and the caller goes on; from
+// then on no wait of the CTA blocks, so the kernel always ends promptly (with a result the host rejects).
+struct WaitLimit {
+    int dead;        // a wait of this CTA gave up
+    unsigned rounds; // failed tries of an mbarrier wait / failed polls of a global word before giving up
+};
+constexpr unsigned WAIT_ROUNDS_DEFAULT = 1u << 23;
+__device__ __forceinline__ void mbar_wait(uint64_t * bar, unsigned parity, int * status, volatile WaitLimit * wl) {
     for (unsigned it = 0; !mbar_try_wait(bar, parity); it++) {
-        if (it >= (1u << 23)) {
+        if (wl->dead) return;
+        if (it >= wl->rounds) {
+            wl->dead = 1;
             if (status) atomicExch(status, (int) KS_WAIT_TIMEOUT);
             return;
         }

@@ -1,6 +1,6 @@
 // Fast decode attention for sm_100a: warp-specialised, register dequantisation, TMA bulk rings, all SMs busy on one sequence.
 //
-// Same arithmetic as the baseline kernel in kv_kernels.cu (the reference's attn_core_t, qwen38_mk.cu:2756-3067): the chunk
+// Same arithmetic as the tensor-core kernel (the reference's attn_core_t, qwen38_mk.cu:2756-3067): the chunk
 // partition attn_dims, 32-position tiles in order inside a chunk with a running max, P rounded to fp16, fp32 accumulation.
 // What changes is who does the work:
 //   - a chunk (up to thousands of positions) is cut into batches of B <= 8 tiles; a batch is a task. With one sequence the
@@ -67,6 +67,7 @@ struct Smem {
     float macc[2][AR];     // the reference max the accumulator rows are scaled to
     uint64_t k_full[SW], v_full[NSV], v_empty[NSV], p_full[NPSLOT], p_empty[NPSLOT];
     AttnJob job; // the CTA's job, copied here once: parameter / global reads stay out of the tile loops
+    WaitLimit wl; // the launch's wait limit and the CTA's give-up flag
 };
 
 struct Args {
@@ -85,6 +86,7 @@ struct Args {
     const AttnTask * tasks; // mode 0, optional: the task list of a kv head built on the host (position-range jobs), else null
     int ntasks;             // tasks per kv head in that list
     unsigned long long * prof; // optional: [CTA][PROF_BATCHES][PROF_STAMPS] globaltimer stamps (null: off)
+    unsigned wait_rounds;      // failed tries of a wait before the CTA gives up
 };
 constexpr int PROF_BATCHES = 16, PROF_STAMPS = 20;
 #define MKKV_STAMP(k)                                                                                                  \
@@ -293,6 +295,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
         sm.macc[0][tid] = sm.macc[1][tid] = -CUDART_INF_F;
     }
     if (tid == 0) {
+        sm.wl.dead = 0;
+        sm.wl.rounds = a.wait_rounds;
         for (int s = 0; s < SW; s++) mbar_init(&sm.k_full[s], 1);
         for (int s = 0; s < NSV; s++) { mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], SW); }
         for (int s = 0; s < NPSLOT; s++) { mbar_init(&sm.p_full[s], 1); mbar_init(&sm.p_empty[s], SW); }
@@ -369,7 +373,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
                 vp_c1 = k.c1;
             }
             const int st = vp_cnt % NSV;
-            mbar_wait(&sm.v_empty[st], ((vp_cnt / NSV) & 1) ^ 1, a.status);
+            mbar_wait(&sm.v_empty[st], ((vp_cnt / NSV) & 1) ^ 1, a.status, &sm.wl);
             issue_tile(vsrc, vp_tb, vp_c1, sm.vst[st], &sm.v_full[st]);
             vp_cnt++;
             vp_tb += ATP;
@@ -393,7 +397,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
             if (dg == 0) MKKV_STAMP(8);
             for (int j = 0; j < SW; j++) {
                 const int ps = (bcnt & 1) * SW + j;
-                mbar_wait(&sm.p_full[ps], (bcnt >> 1) & 1, a.status);
+                mbar_wait(&sm.p_full[ps], (bcnt >> 1) & 1, a.status, &sm.wl);
                 if (dg == 0 && j == 0) MKKV_STAMP(9);
                 const PSlot & P = sm.ps[ps];
                 if (P.valid) {
@@ -403,7 +407,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
                     __syncwarp();
                     const int st = vcnt % NSV, tb = k.pos0 + j * ATP, np = min(ATP, k.c1 - tb);
                     if (dg == 0 && j < 2) MKKV_STAMP(12 + 3 * j);
-                    mbar_wait(&sm.v_full[st], (vcnt / NSV) & 1, a.status);
+                    mbar_wait(&sm.v_full[st], (vcnt / NSV) & 1, a.status, &sm.wl);
                     if (dg == 0 && j < 2) MKKV_STAMP(13 + 3 * j);
                     if (P.rescale[0] | P.rescale[1]) {
 #pragma unroll
@@ -468,7 +472,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
                     for (int j = 0; j < 4; j++)
 #pragma unroll
                         for (int q = 0; q < 4; q++) acc[i][j][q] = 0.f;
-                mbar_wait(&sm.k_full[warp], kuse & 1, a.status);
+                mbar_wait(&sm.k_full[warp], kuse & 1, a.status, &sm.wl);
                 kuse++;
                 if (warp == 0) MKKV_STAMP(1);
 #if !(MKKV_ABL & 2)
@@ -524,16 +528,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
                             if (k.b > 0) {
                                 const unsigned long long * src = xm + (size_t) (k.b - 1) * AR;
                                 unsigned long long w = __ldcv(src);
-                                if ((unsigned) (w >> 32) != (unsigned) a.epoch) {
-                                    const unsigned long long t0 = globaltimer_ns();
-                                    for (unsigned it = 0;; it++) {
-                                        w = __ldcv(src);
-                                        if ((unsigned) (w >> 32) == (unsigned) a.epoch) break;
-                                        if ((it & 255u) == 255u && globaltimer_ns() - t0 > 2000000000ull) {
-                                            atomicExch(a.status, (int) KS_WAIT_TIMEOUT);
-                                            break;
-                                        }
+                                for (unsigned it = 0; (unsigned) (w >> 32) != (unsigned) a.epoch; it++) {
+                                    if (sm.wl.dead) break;
+                                    if (it >= sm.wl.rounds) {
+                                        sm.wl.dead = 1;
+                                        atomicExch(a.status, (int) KS_WAIT_TIMEOUT);
+                                        break;
                                     }
+                                    w = __ldcv(src);
                                 }
                                 m_in = __uint_as_float((unsigned) w);
                             }
@@ -549,7 +551,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_fast_kernel(const __grid_con
                 }
                 if (warp == 0) MKKV_STAMP(5);
                 // the slots of this batch must have been released by the P V warps (two batches ago)
-                for (int j = 0; j < SW; j++) mbar_wait(&sm.p_empty[(bcnt & 1) * SW + j], ((bcnt >> 1) & 1) ^ 1, a.status);
+                for (int j = 0; j < SW; j++) mbar_wait(&sm.p_empty[(bcnt & 1) * SW + j], ((bcnt >> 1) & 1) ^ 1, a.status, &sm.wl);
                 float m_ref = m_in;
                 for (int j = 0; j < k.nt; j++) {
                     PSlot & Pj = sm.ps[(bcnt & 1) * SW + j];
@@ -697,6 +699,7 @@ cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_ho
     a.nbmax = nbmax;
     a.epoch = epoch;
     a.status = status;
+    a.wait_rounds = attn_common::WAIT_ROUNDS_DEFAULT;
     int grid;
     AttnJob merge_job = jobs_host[0];
     if (njobs == 1 && spread) {

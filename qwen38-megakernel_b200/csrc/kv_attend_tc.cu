@@ -71,6 +71,7 @@ constexpr int NRAW = 9;
 constexpr int OP_SLOT = GP * 128 * 2;       // fp16 operand: 128 positions x 128 dims
 constexpr int NOP = 3;
 constexpr int NSB = 5;                      // S^T buffers: K runs NSB groups ahead of V
+constexpr int NTASK = 16;
 constexpr int Q_BYTES = AR * HD * 2, P_BYTES = AR * GP * 2;
 constexpr unsigned S_COL = 0, S_STRIDE = 64, O_COL0 = NSB * 64, O_COL1 = O_COL0 + 2 * AR, TMEM_COLS = 512; // an O^T half: 48 columns for P's high part, 48 for its low part
 static_assert(O_COL1 + 2 * AR <= TMEM_COLS, "tensor-memory columns");
@@ -103,8 +104,9 @@ struct Smem {
     unsigned char rtok[AR];     // token of a query row
     unsigned tmem_base;
     WaitCtl wc;                 // the launch's wait limits; dead: a wait of this CTA gave up, no later wait blocks
-    AttnTask tasks[8];          // the CTA's groups as the producer reaches them, by group % 8 (no role is 8 groups apart from it)
-    uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[NSB], s_empty[NSB], p_full, p_empty;
+    AttnTask tasks[NTASK];      // the CTA's groups as the producer reaches them, by group % NTASK (no role is that far from it:
+                                // the producer's K is at most NSB + 2 groups ahead of the softmax warps' group)
+    uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[NSB], s_empty[NSB], p_full, p_empty, fin;
     AttnJob job;
 };
 
@@ -244,71 +246,112 @@ __device__ __forceinline__ float exp_neg(float x) {
 }
 
 // ---- one worker step: position `row` of a staged tile, dims 32 jb .. 32 jb + 31 -> four 16-byte operand units ----
-// A unit holds the 8 values of one lane word in the order UNIT_PERM (kv_unpack.h). dst: the thread's unit of dim group 4 (jb & 3)
-// of the slot; the next dim groups are 2048 bytes apart. valid false (a row past the chunk end holds stale bytes): zeros.
+// A unit holds the 8 values of one lane word in the order UNIT_PERM (kv_unpack.h: pair_words and friends are the host-checkable
+// statement of what follows). The instructions are chosen by hand -- one AND-OR per pair for the high bits under the bias, one for
+// the nibbles, a subtract and a multiply in fp16 pairs -- because the compiler re-associates the plain C form into half as many
+// again. raw, dst: shared-space addresses; dst: the thread's unit of dim group 4 (jb & 3) of the slot, the next dim groups are 2048
+// bytes apart. valid false (a row past the chunk end holds stale bytes): zeros.
+__device__ __forceinline__ unsigned and_or(unsigned a, unsigned mask, unsigned c) { // (a & mask) | c
+    unsigned d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
+    return d;
+}
+template <unsigned MASK> __device__ __forceinline__ unsigned and_or_imm(unsigned a, unsigned c) { // (a & MASK) | c, the mask an immediate
+    unsigned d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "n"(MASK), "r"(c));
+    return d;
+}
 // fp16(d * q) of a pair held as (bias + n): the difference is exact, the product is rounded once
-__device__ __forceinline__ unsigned pair_val(unsigned x, unsigned sub, __half2 d) {
-    const __half2 h = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&x), *reinterpret_cast<const __half2 *>(&sub)), d);
-    return *reinterpret_cast<const unsigned *>(&h);
+template <unsigned SUB> __device__ __forceinline__ unsigned pair_val(unsigned x, unsigned d) {
+    unsigned r;
+    asm("{\n\t.reg .b32 t;\n\tsub.f16x2 t, %1, %2;\n\tmul.f16x2 %0, t, %3;\n\t}" : "=r"(r) : "r"(x), "r"(SUB), "r"(d));
+    return r;
 }
-template <int BITS> __device__ __forceinline__ void store_unit(uint8_t * dst, const unsigned (&x)[4], __half2 d) {
-    const unsigned sa = pair_sub_a<BITS>(), sb = BITS >= 7 ? sa : pair_sub_b<BITS>();
-    *reinterpret_cast<uint4 *>(dst) = make_uint4(pair_val(x[0], sa, d), pair_val(x[1], sb, d), pair_val(x[2], sa, d), pair_val(x[3], sb, d));
+__device__ __forceinline__ void sts128(unsigned addr, unsigned a, unsigned b, unsigned c, unsigned d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-template <int BITS> __device__ __forceinline__ void dq_item(const uint8_t * raw, int row, int jb, bool valid, uint8_t * dst) {
-    const __half dsc = valid ? reinterpret_cast<const __half *>(raw + TILE_SC_OFF)[row * 8 + jb] : __float2half_rn(0.f);
-    const __half2 d = __half2half2(dsc);
-    const uint8_t * rp = raw + row * (32 * BITS);
-    unsigned x[4];
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(unsigned addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned lds32(unsigned addr) {
+    unsigned v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned lds16(unsigned addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+    return v;
+}
+// one unit: the pairs' high-bit words y0 .. y3 (bias included) and the lane word -> four values, stored
+template <int BITS> __device__ __forceinline__ void unit_out(unsigned dst, unsigned word, unsigned y0, unsigned y1, unsigned y2, unsigned y3, unsigned d) {
+    constexpr unsigned SA = MAGIC_A + (0x00010001u << (BITS - 1)), SB = MAGIC_B + (0x00100010u << (BITS - 1));
+    const unsigned w8 = word >> 8;
+    sts128(dst, pair_val<SA>(and_or_imm<NIB_A>(word, y0), d), pair_val<SB>(and_or_imm<NIB_B>(word, y1), d),
+           pair_val<SA>(and_or_imm<NIB_A>(w8, y2), d), pair_val<SB>(and_or_imm<NIB_B>(w8, y3), d));
+}
+template <int BITS> __device__ __forceinline__ void dq_item(unsigned raw, int row, int jb, bool valid, unsigned dst) {
+    const unsigned sc = valid ? lds16(raw + TILE_SC_OFF + (row * 8 + jb) * 2) : 0u;
+    const unsigned d = sc | (sc << 16);
+    const unsigned rp = raw + row * (32 * BITS);
     if constexpr (BITS == 8) {
-        const uint4 v0 = *reinterpret_cast<const uint4 *>(rp + 32 * jb), v1 = *reinterpret_cast<const uint4 *>(rp + 32 * jb + 16);
+        const uint4 v0 = lds128(rp + 32 * jb), v1 = lds128(rp + 32 * jb + 16);
         const unsigned w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        constexpr unsigned S8 = MAGIC_A + 0x00800080u;
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const unsigned lo = w[2 * u] ^ 0x80808080u, hi = w[2 * u + 1] ^ 0x80808080u; // q + 128
-            x[0] = __byte_perm(lo, MAGIC_A, 0x7270); // (value 0, value 2) under the exponent of 1024
-            x[1] = __byte_perm(hi, MAGIC_A, 0x7270); // (4, 6)
-            x[2] = __byte_perm(lo, MAGIC_A, 0x7371); // (1, 3)
-            x[3] = __byte_perm(hi, MAGIC_A, 0x7371); // (5, 7)
-            store_unit<8>(dst + u * 2048, x, d);
+            sts128(dst + u * 2048, pair_val<S8>(__byte_perm(lo, MAGIC_A, 0x7270), d), // (value 0, value 2) under the exponent of 1024
+                   pair_val<S8>(__byte_perm(hi, MAGIC_A, 0x7270), d),                 // (4, 6)
+                   pair_val<S8>(__byte_perm(lo, MAGIC_A, 0x7371), d),                 // (1, 3)
+                   pair_val<S8>(__byte_perm(hi, MAGIC_A, 0x7371), d));                // (5, 7)
         }
     } else {
-        const uint4 nv = *reinterpret_cast<const uint4 *>(rp + 16 * jb);
+        const uint4 nv = lds128(rp + 16 * jb);
         const unsigned nw[4] = {nv.x, nv.y, nv.z, nv.w};
         if constexpr (BITS == 4) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                pair_words<4>(nw[u], 0u, x);
-                store_unit<4>(dst + u * 2048, x, d);
-            }
+            for (int u = 0; u < 4; u++) unit_out<4>(dst + u * 2048, nw[u], MAGIC_A, MAGIC_B, MAGIC_A, MAGIC_B, d);
         } else if constexpr (BITS == 5) {
-            const unsigned h = *reinterpret_cast<const unsigned *>(rp + 128 + 4 * jb);
+            const unsigned h = lds32(rp + 128 + 4 * jb);
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-                pair_words<5>(nw[u], __byte_perm(h, 0u, 0x4440 + u), x);
-                store_unit<5>(dst + u * 2048, x, d);
+                // bit k of the word's byte of high bits at 4 + k and 18 + k; the copy one lower serves the odd values
+                const unsigned hb = __byte_perm(h, 0u, 0x4440 + u), t = hb * 0x00040010u, t1 = hb * 0x00020008u;
+                unit_out<5>(dst + u * 2048, nw[u], and_or_imm<0x00100010u>(t, MAGIC_A), and_or_imm<0x01000100u>(t, MAGIC_B),
+                            and_or_imm<0x00100010u>(t1, MAGIC_A), and_or_imm<0x01000100u>(t1, MAGIC_B), d);
             }
         } else if constexpr (BITS == 6) {
-            const uint2 h = *reinterpret_cast<const uint2 *>(rp + 128 + 8 * jb);
-            const unsigned hw[4] = {h.x, h.x >> 16, h.y, h.y >> 16}; // (pair_words masks the fields it reads)
+            const uint2 h = lds64(rp + 128 + 8 * jb);
+            const unsigned hw[4] = {h.x, h.x >> 16, h.y, h.y >> 16};
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-                pair_words<6>(nw[u], hw[u], x);
-                store_unit<6>(dst + u * 2048, x, d);
+                // even values' 2-bit fields at bits 0, 4, 8, 12 of he, odd values' of ho: the gaps keep the shifted copies' sums apart
+                const unsigned he = hw[u] & 0x3333u, ho = (hw[u] >> 2) & 0x3333u;
+                unit_out<6>(dst + u * 2048, nw[u], and_or_imm<0x00300030u>(he * 0x00010010u, MAGIC_A), and_or_imm<0x03000300u>(he * 0x00001001u, MAGIC_B),
+                            and_or_imm<0x00300030u>(ho * 0x00010010u, MAGIC_A), and_or_imm<0x03000300u>(ho * 0x00001001u, MAGIC_B), d);
             }
-        } else {
-            const unsigned * hp = reinterpret_cast<const unsigned *>(rp + 128 + 12 * jb);
-            const unsigned h0 = hp[0], h1 = hp[1], h2 = hp[2];
+        } else { // 7 bits: every pair under the 1024 bias (pair_words7)
+            const unsigned h0 = lds32(rp + 128 + 12 * jb), h1 = lds32(rp + 132 + 12 * jb), h2 = lds32(rp + 136 + 12 * jb);
             const unsigned hw[4] = {h0, __funnelshift_r(h0, h1, 24), __funnelshift_r(h1, h2, 16), h2 >> 8}; // (bits above 23: not read)
+            constexpr unsigned S7 = MAGIC_A + 0x00400040u;
 #pragma unroll
             for (int u = 0; u < 4; u++) {
+                unsigned x[4];
                 pair_words7(nw[u], hw[u], x);
-                store_unit<7>(dst + u * 2048, x, d);
+                sts128(dst + u * 2048, pair_val<S7>(x[0], d), pair_val<S7>(x[1], d), pair_val<S7>(x[2], d), pair_val<S7>(x[3], d));
             }
         }
     }
 }
-__device__ __forceinline__ void dq_item_any(int bits, const uint8_t * raw, int row, int jb, bool valid, uint8_t * dst) {
+__device__ __forceinline__ void dq_item_any(int bits, unsigned raw, int row, int jb, bool valid, unsigned dst) {
     switch (bits) {
     case 4: dq_item<4>(raw, row, jb, valid, dst); break;
     case 5: dq_item<5>(raw, row, jb, valid, dst); break;
@@ -318,12 +361,12 @@ __device__ __forceinline__ void dq_item_any(int bits, const uint8_t * raw, int r
     }
 }
 
-// order-preserving map float <-> int (for redux.sync.max)
-__device__ __forceinline__ int f2key(float x) {
-    const int i = __float_as_int(x);
-    return i ^ ((i >> 31) & 0x7fffffff);
+// max over the warp (sm_100a: redux.sync on fp32)
+__device__ __forceinline__ float warp_max(float x) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+    return r;
 }
-__device__ __forceinline__ float key2f(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 
 // bounded poll of an exchange word until it carries this launch's tag
 __device__ __forceinline__ float poll_word(const unsigned long long * src, unsigned long long w, int epoch, volatile WaitCtl * wc, int * status) {
@@ -368,8 +411,10 @@ __device__ __forceinline__ Task make_task4(const Geo4 & G4, int t) {
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_constant__ Args a) {
-    extern __shared__ uint8_t smem_raw[];
-    Smem & sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t) 127);
+    // (the dynamic shared memory starts on a 128-byte boundary -- there is no static shared memory in this kernel --, which is all the
+    // bulk copies, matrix descriptors and barriers need; no pointer arithmetic here, so every access below is a shared-space one)
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    Smem & sm = *reinterpret_cast<Smem *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     {
         const AttnJob * Jp = &a.one;
@@ -388,6 +433,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         for (int s = 0; s < NSB; s++) { mbar_init(&sm.s_full[s], 1); mbar_init(&sm.s_empty[s], NSOFT); }
         mbar_init(&sm.p_full, NSOFT);
         mbar_init(&sm.p_empty, 1);
+        mbar_init(&sm.fin, 1);
         sm.wc.dead = 0;
         sm.wc.hint = a.wait_hint_ns;
         sm.wc.rounds = a.wait_rounds;
@@ -434,7 +480,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             if (kv.s[0].rot) fwht256(v, lane);
             __half2 * h = reinterpret_cast<__half2 *>(&out);
 #pragma unroll
-            for (int k = 0; k < 4; k++) h[k] = __floats2half2_rn(__fmul_rn(v[2 * k], 0.0625f), __fmul_rn(v[2 * k + 1], 0.0625f));
+            for (int k = 0; k < 4; k++) // the unit's dims in the order the unpack warps leave K's (unit_perm)
+                h[k] = __floats2half2_rn(__fmul_rn(v[unit_perm(2 * k)], 0.0625f), __fmul_rn(v[unit_perm(2 * k + 1)], 0.0625f));
         }
         *reinterpret_cast<uint4 *>(sm.q + lane * (AR / 8 * 128) + (r >> 3) * 128 + (r & 7) * 16) = out;
     }
@@ -448,39 +495,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
     if (warp >= W_ISSUE) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 " MKKV_TC_REGS_CTL ";");
     if (warp == W_PROD) {
-        // ---- producer: K(0), K(1), K(2), then V(i), K(i + 3) -- the order the unpack warps consume ----
-        if (lane == 0) {
+        // ---- producer: K(0) .. K(NSB - 1), then V(i), K(i + NSB) -- the order the unpack warps consume. Lanes 0 .. 3 fetch one
+        // tile of the group each ----
+        if (lane < GT) {
             const SideSrc ksrc = make_src(kv, 0, g, ws), vsrc = make_src(kv, 1, g, ws);
-            unsigned rseq = 0;
-            for (int nk = 0, nv = 0; nv < G;) { // K runs NSB groups ahead of V
+            unsigned rseq = lane; // this lane's tile in the sequence of all tiles of all side-groups
+            unsigned issued = 0xffffffu; // the lane's last three copies as bytes (slot << 1 | phase parity), 0xff: none
+            for (int nk = 0, nv = 0; nv < G && !sm.wc.dead;) {
                 const bool isK = nk < G && nk < nv + NSB;
                 Task k;
                 if (isK) { // a group's K comes first: its task is computed here, once, and left for the other roles (the waits on
                            // the copies' barriers order their reads after this write)
                     k = get_task(kk + nk * tstep);
-                    sm.tasks[nk & 7] = k;
+                    if (lane == 0) sm.tasks[nk % NTASK] = k;
                 } else {
-                    k = sm.tasks[nv & 7];
+                    k = sm.tasks[nv % NTASK];
                 }
+                __syncwarp(0xfu);
                 const SideSrc & S = isK ? ksrc : vsrc;
-                for (int qq = 0; qq < GT; qq++, rseq++) {
-                    const int rs = rseq % NRAW;
-                    const unsigned round = rseq / NRAW;
-                    if (round > 0) tc_wait(&sm.raw_empty[rs], (round - 1) & 1, &sm.wc, a.status);
-                    if (qq < k.nt) issue_tile(S, k.pos0 + qq * ATP, k.c1, sm.raw[rs], &sm.raw_full[rs]);
-                    else mbar_arrive(&sm.raw_full[rs]);
+                const int rs = rseq % NRAW;
+                const unsigned round = rseq / NRAW;
+                if (round > 0) tc_wait(&sm.raw_empty[rs], (round - 1) & 1, &sm.wc, a.status);
+                if (sm.wc.dead) break; // (nothing is fetched into a slot that may still be read, no barrier is over-subscribed)
+                if (lane < k.nt) {
+                    issue_tile(S, k.pos0 + lane * ATP, k.c1, sm.raw[rs], &sm.raw_full[rs]);
+                    issued = (issued << 8) | ((unsigned) rs << 1) | (round & 1u);
+                } else {
+                    mbar_arrive(&sm.raw_full[rs]);
                 }
+                rseq += GT;
                 if (isK) nk++;
                 else nv++;
             }
+            // a CTA whose waits gave up reaches this point with copies possibly in flight: they must land before the CTA's shared
+            // memory is released (bounded; in a normal run every copy was waited for by its consumer long ago)
+            if (sm.wc.dead)
+                for (int j = 0; j < 3; j++) {
+                    const unsigned e = (issued >> (8 * j)) & 0xffu;
+                    if (e == 0xffu) continue;
+                    for (unsigned it = 0; it < (1u << 14) && !mbar_try_wait_hint(&sm.raw_full[e >> 1], e & 1u, 1000u); it++) {}
+                }
         }
     } else if (warp == W_ISSUE) {
-        // ---- issuer: S(0), S(1), S(2), then PV(i), S(i + 3) ----
+        // ---- issuer: S(0) .. S(NSB - 1), then PV(i), S(i + NSB) ----
         if (lane == 0) {
             unsigned oseq = 0;
             const unsigned q_lo = desc_lo(smem_u32(sm.q), AR / 8 * 128), p_lo0 = desc_lo(smem_u32(sm.p[0]), 128);
             const unsigned hi_k = desc_hi(128), hi_mn = desc_hi(2048); // K-major: 8-row groups 128 bytes apart; MN-major: 2048
-            for (int nk = 0, nv = 0; nv < G;) {
+            for (int nk = 0, nv = 0; nv < G && !sm.wc.dead;) {
                 const bool isK = nk < G && nk < nv + NSB;
                 if (isK) { // S^T(nk) = K Q^T
                     const int sb = nk % NSB;
@@ -520,6 +582,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     nv++;
                 }
             }
+            // every instruction issued above is complete before the tensor memory is freed and the CTA's shared memory released
+            // (bounded; in a normal run the softmax warps have already waited for the last one)
+            umma_commit(&sm.fin);
+            for (unsigned it = 0; it < (1u << 14) && !mbar_try_wait_hint(&sm.fin, 0u, 1000u); it++) {}
         }
     }
     } else if (warp >= NSOFT) {
@@ -530,14 +596,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         const bool st = w == 0;
         int rs = q, rph = 0, os = 0, oph = 0; // raw slot / phase of this warp's tile, operand slot / phase
         bool owrap = false;
-        for (int nk = 0, nv = 0; nv < G;) {
+        for (int nk = 0, nv = 0; nv < G && !sm.wc.dead;) {
             const bool isK = nk < G && nk < nv + NSB;
             const int side = isK ? 0 : 1, grp = isK ? nk - NSB : nv;
             (void) grp; // (the stamps' group index)
             if (st) TC_STAMP(grp, side ? 8 : 11);
             tc_wait(&sm.raw_full[rs], rph, &sm.wc, a.status);
             if (st) TC_STAMP(grp, side ? 9 : 12);
-            const AttnTask & kr = sm.tasks[(isK ? nk : nv) & 7];
+            const AttnTask & kr = sm.tasks[(isK ? nk : nv) % NTASK];
             const int k_pos0 = kr.pos0;
             const int2 kt = *reinterpret_cast<const int2 *>(&kr.c1); // c1, nt
             const int tbq = k_pos0 + q * ATP;
@@ -550,7 +616,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
 #pragma unroll 1
             for (int h = 0; h < 2; h++) {
                 if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.wc, a.status);
-                dq_item_any(bits, sm.raw[rs], lane, 4 * h + jr, valid, sm.op[os] + 4 * jr * 2048 + pos_off);
+                dq_item_any(bits, smem_u32(sm.raw[rs]), lane, 4 * h + jr, valid, smem_u32(sm.op[os]) + 4 * jr * 2048 + pos_off);
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.op_full[os]);
@@ -580,6 +646,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         float m_acc = -CUDART_INF_F, carry = -CUDART_INF_F; // (carry: batch mode, the chunk's running max after the previous group)
         unsigned long long w0 = 0, w1 = 0, w2 = 0;
         auto xbase = [&](const Task & k) -> size_t { return (((size_t) g * ATT_NCH + k.c) * a.nbmax) * AR + r_own; };
+        // the exchange arrays are only touched by a CTA that has not given up (after a give-up the task records of groups the
+        // producer never reached are not valid) and only inside their bounds
+        auto exch_ok = [&](const Task & k) -> bool { return !sm.wc.dead && (unsigned) k.c < (unsigned) ATT_NCH && (unsigned) k.b < (unsigned) a.nbmax; };
         // which of the warp's rows this thread's position must not see in group k: row token t sees positions <= n + t; positions
         // past the chunk end and padding rows see nothing (0 for almost every group: uniform test first)
         auto row_mask = [&](const Task & k) -> unsigned {
@@ -610,7 +679,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         auto maxima = [&](int j) {
             if (st) TC_STAMP(j, 0);
             tc_wait(&sm.s_full[j % NSB], (j / NSB) & 1, &sm.wc, a.status);
-            const Task k = sm.tasks[j & 7];
+            const Task k = sm.tasks[j % NTASK];
             if (st) TC_STAMP(j, 1);
             tc_fence_after();
             unsigned rq[RS / 8][8];
@@ -621,27 +690,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             for (int gq = 0; gq < RS / 8; gq++) {
                 float s[8];
                 scores_take(rq[gq], mask, gq, s);
-                int kx[8];
+                float mx[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) kx[i] = __reduce_max_sync(FULL_MASK, f2key(s[i]));
+                for (int i = 0; i < 8; i++) mx[i] = warp_max(s[i]);
                 if (lane == 0) {
-                    int4 * d = reinterpret_cast<int4 *>(&sm.tmax[j % 3][q][row0 + 8 * gq]);
-                    d[0] = make_int4(kx[0], kx[1], kx[2], kx[3]);
-                    d[1] = make_int4(kx[4], kx[5], kx[6], kx[7]);
+                    float4 * d = reinterpret_cast<float4 *>(&sm.tmax[j % 3][q][row0 + 8 * gq]);
+                    d[0] = make_float4(mx[0], mx[1], mx[2], mx[3]);
+                    d[1] = make_float4(mx[4], mx[5], mx[6], mx[7]);
                 }
             }
             named_bar(1 + c2, GT * 32);
-            if (!batch && owner && q == 0 && k.nb > 1 && k.b + 1 < k.nb) {
-                const int(&tm)[GT][AR] = sm.tmax[j % 3];
-                const int gk = max(max(tm[0][r_own], tm[1][r_own]), max(tm[2][r_own], tm[3][r_own]));
-                __stcg(a.xa + xbase(k) + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(key2f(gk)));
+            if (!batch && owner && q == 0 && k.nb > 1 && k.b + 1 < k.nb && exch_ok(k)) {
+                const float(&tm)[GT][AR] = sm.tmax[j % 3];
+                const float gk = fmaxf(fmaxf(tm[0][r_own], tm[1][r_own]), fmaxf(tm[2][r_own], tm[3][r_own]));
+                __stcg(a.xa + xbase(k) + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(gk));
             }
             if (st) TC_STAMP(j, 2);
         };
         // the words the running max of group k will need: requested one phase before they are used, when the CTAs that hold
         // the chunk's previous groups have most likely published them
         auto request_words = [&](const Task & k) {
-            if (!batch && owner && k.nb > 1) {
+            if (!batch && owner && k.nb > 1 && exch_ok(k)) {
                 const size_t xb0 = xbase(k);
                 if (k.b >= 1) w1 = __ldcv(a.xa + xb0 + (size_t) (k.b - 1) * AR);
                 if (k.b >= 2) w2 = __ldcv(a.xa + xb0 + (size_t) (k.b - 2) * AR);
@@ -655,23 +724,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             if (owner) {
                 float m_in = batch && k.b > 0 ? carry : -CUDART_INF_F;
                 const size_t xb0 = xbase(k);
-                if (!batch && k.nb > 1) {
+                const bool alive = exch_ok(k);
+                if (alive && !batch && k.nb > 1) {
                     if (k.b >= 1) m_in = poll_word(a.xa + xb0 + (size_t) (k.b - 1) * AR, w1, a.epoch, &sm.wc, a.status);
                     if (k.b >= 2) m_in = fmaxf(m_in, poll_word(a.xa + xb0 + (size_t) (k.b - 2) * AR, w2, a.epoch, &sm.wc, a.status));
                     if (k.b >= 3) m_in = fmaxf(m_in, poll_word(a.xb + xb0 + (size_t) (k.b - 3) * AR, w0, a.epoch, &sm.wc, a.status));
                 }
                 if (st) TC_STAMP(i, 7);
-                const int(&tm)[GT][AR] = sm.tmax[i % 3];
-                int kr = f2key(m_in), kM;
+                const float(&tm)[GT][AR] = sm.tmax[i % 3];
+                float mr = m_in; // running max after this warp's tile, M: after the whole group
 #pragma unroll
                 for (int t = 0; t < GT; t++)
-                    if (t <= q) kr = max(kr, tm[t][r_own]);
-                kM = kr;
+                    if (t <= q) mr = fmaxf(mr, tm[t][r_own]);
+                float M = mr;
 #pragma unroll
                 for (int t = 0; t < GT; t++)
-                    if (t > q) kM = max(kM, tm[t][r_own]);
-                const float mr = key2f(kr), M = key2f(kM);
-                if (!batch && q == 0 && k.nb > 1 && k.b + 3 < k.nb) __stcg(a.xb + xb0 + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(M));
+                    if (t > q) M = fmaxf(M, tm[t][r_own]);
+                if (alive && !batch && q == 0 && k.nb > 1 && k.b + 3 < k.nb) __stcg(a.xb + xb0 + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(M));
                 carry = M;
                 if (M != -CUDART_INF_F) {
                     if (m_acc == -CUDART_INF_F) m_acc = M + REF_MARGIN;
@@ -697,30 +766,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             const unsigned anyf = __ballot_sync(FULL_MASK, owner && f != 1.f);
             __syncwarp();
             if (st) TC_STAMP(i, 4);
-            if (i > 0) tc_wait(&sm.p_empty, (i - 1) & 1, &sm.wc, a.status); // P V of the previous group is complete: P is free, O^T at rest
-            if (st) TC_STAMP(i, 5);
-            tc_fence_after();
-#if MKKV_TC_PROF
-            if (anyf && a.prof && st && lane == 0) a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 15] += 1ull | ((unsigned long long) __popc(anyf) << 32);
-#endif
-            if (anyf) { // a reference max moved: bring this warp's block of the accumulator (and its row sums) to it
-#pragma unroll 1
-                for (int hg = 0; hg < 4 * (RS / 8); hg++) { // (half, high / low block, 8 columns)
-                    const int h = hg / (2 * (RS / 8)), pt = (hg / (RS / 8)) & 1, gq = hg % (RS / 8);
-                    if (!((anyf >> (8 * gq)) & 0xffu)) continue; // no row of these 8 moved
-                    const unsigned ad = lane_addr + (h ? O_COL1 : O_COL0) + AR * pt + row0 + 8 * gq;
-                    float v[8];
-                    tmem_ld8(ad, v);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) v[j] *= W.f[8 * gq + j];
-                    tmem_st8(ad, v);
-                }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            if (anyf) { // a reference max moved: the row sums follow at once, the accumulator when it is at rest (below)
 #pragma unroll
                 for (int j = 0; j < RS; j++) l_acc[j] *= W.f[j];
             }
+            // P of the group into registers: the exponentials do not wait for the P buffer
             const unsigned mask = row_mask(k);
-            unsigned ra[8], rb[8];
+            unsigned ra[8], rb[8], hi[RS / 8][4], lo[RS / 8][4];
             scores_request(i, 0, ra);
 #pragma unroll
             for (int gq = 0; gq < RS / 8; gq++) { // row groups of 8: one 16-byte unit of each P part; the next group's scores are in
@@ -747,7 +799,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                 const uint4 bhv = *reinterpret_cast<const uint4 *>(&W.bh[4 * gq]), blv = *reinterpret_cast<const uint4 *>(&W.bl[4 * gq]);
                 const float mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w}, be[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
                 const unsigned bhw[4] = {bhv.x, bhv.y, bhv.z, bhv.w}, blw[4] = {blv.x, blv.y, blv.z, blv.w};
-                unsigned hi[4], lo[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const int r = 8 * gq + 2 * j;
@@ -758,12 +809,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     const __half2 bh = *reinterpret_cast<const __half2 *>(&bhw[j]), bl = *reinterpret_cast<const __half2 *>(&blw[j]);
                     const __half2 hh = __hmul2(ph, bh);                 // P beta = hh + ll up to 2^-22: the product's exact residual
                     const __half2 ll = __hfma2(ph, bl, __hfma2(ph, bh, __hneg2(hh))); // plus the low part of beta
-                    hi[j] = *reinterpret_cast<const unsigned *>(&hh);
-                    lo[j] = *reinterpret_cast<const unsigned *>(&ll);
+                    hi[gq][j] = *reinterpret_cast<const unsigned *>(&hh);
+                    lo[gq][j] = *reinterpret_cast<const unsigned *>(&ll);
                 }
+            }
+            if (st && i < 15) TC_STAMP(i, 15);
+            if (i > 0) tc_wait(&sm.p_empty, (i - 1) & 1, &sm.wc, a.status); // P V of the previous group is complete: P is free, O^T at rest
+            if (st) TC_STAMP(i, 5);
+            tc_fence_after();
+#if MKKV_TC_PROF
+            if (anyf && a.prof && st && lane == 0) a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 15] += 1ull | ((unsigned long long) __popc(anyf) << 32);
+#endif
+            if (anyf) { // bring this warp's block of the accumulator to the moved reference max
+#pragma unroll 1
+                for (int hg = 0; hg < 4 * (RS / 8); hg++) { // (half, high / low block, 8 columns)
+                    const int h = hg / (2 * (RS / 8)), pt = (hg / (RS / 8)) & 1, gq = hg % (RS / 8);
+                    if (!((anyf >> (8 * gq)) & 0xffu)) continue; // no row of these 8 moved
+                    const unsigned ad = lane_addr + (h ? O_COL1 : O_COL0) + AR * pt + row0 + 8 * gq;
+                    float v[8];
+                    tmem_ld8(ad, v);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] *= W.f[8 * gq + j];
+                    tmem_st8(ad, v);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+#pragma unroll
+            for (int gq = 0; gq < RS / 8; gq++) {
                 const unsigned off = (unsigned) ((RS / 8) * c2 + gq) * 2048 + pos_off;
-                *reinterpret_cast<uint4 *>(sm.p[0] + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4 *>(sm.p[1] + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4 *>(sm.p[0] + off) = make_uint4(hi[gq][0], hi[gq][1], hi[gq][2], hi[gq][3]);
+                *reinterpret_cast<uint4 *>(sm.p[1] + off) = make_uint4(lo[gq][0], lo[gq][1], lo[gq][2], lo[gq][3]);
             }
             fence_async_smem();
             tc_fence_before();
@@ -776,18 +851,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             for (int i = -1; i < G; i++) { // maxima of group i + 1, then P of group i (tasks: left by the producer, see there)
                 if (i + 1 < G) maxima(i + 1);
                 if (i >= 0) {
-                    const Task kc = sm.tasks[i & 7];
+                    const Task kc = sm.tasks[i % NTASK];
                     softmax(i, kc);
                 }
                 if (i + 1 < G) {
-                    const Task kn = sm.tasks[(i + 1) & 7];
+                    const Task kn = sm.tasks[(i + 1) % NTASK];
                     request_words(kn);
                 }
             }
             tc_wait(&sm.p_empty, (G - 1) & 1, &sm.wc, a.status);
             tc_fence_after();
         }
-        // ---- the CTA's partial: O^T lanes are dims, columns are query rows ----
+        // ---- the CTA's partial: O^T lanes are dims (in the unpacked units' order: mapped back here), columns are query rows ----
+        const int pdim = (prow & ~7) | unit_perm(prow & 7);
 #pragma unroll
 #pragma unroll 1
         for (int hg = 0; hg < 2 * (RS / 8); hg++) {
@@ -800,7 +876,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const int r = row0 + 8 * gq + j;
-                if (r < R) a.part[((size_t) slot * AR + r) * HD + 128 * h + prow] = G > 0 ? v[j] + w[j] : 0.f;
+                if (r < R) a.part[((size_t) slot * AR + r) * HD + 128 * h + pdim] = G > 0 ? v[j] + w[j] : 0.f;
             }
         }
 #pragma unroll
@@ -851,7 +927,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
 
 } // namespace tc
 
+static_assert(sizeof(tc::Smem) + 128 <= 232448, "shared memory of one CTA");
 size_t attend_tc_smem_bytes() { return sizeof(tc::Smem) + 128; }
+// the wait limits of the launches that follow (process-wide; diagnostics and the failure-path test)
+static unsigned g_wait_hint_ns = tc::WAIT_HINT_NS, g_wait_rounds = tc::WAIT_ROUNDS, g_poll_rounds = tc::POLL_ROUNDS;
+void attend_tc_set_wait_limits(unsigned hint_ns, unsigned rounds, unsigned polls) {
+    g_wait_hint_ns = hint_ns;
+    g_wait_rounds = rounds;
+    g_poll_rounds = polls;
+}
+void attend_tc_default_wait_limits() { attend_tc_set_wait_limits(tc::WAIT_HINT_NS, tc::WAIT_ROUNDS, tc::POLL_ROUNDS); }
 cudaError_t preload_attend_tc() {
     cudaFuncAttributes fa;
     return cudaFuncGetAttributes(&fa, (const void *) tc::attn_tc_kernel);
@@ -885,6 +970,9 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
     a.nbmax = nbmax;
     a.epoch = epoch;
     a.status = status;
+    a.wait_hint_ns = g_wait_hint_ns;
+    a.wait_rounds = g_wait_rounds;
+    a.poll_rounds = g_poll_rounds;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -932,6 +1020,9 @@ cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * job
     a.done = nullptr;
     a.done_target = 0;
     a.prof = nullptr;
+    a.wait_hint_ns = g_wait_hint_ns;
+    a.wait_rounds = g_wait_rounds;
+    a.poll_rounds = g_poll_rounds;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

@@ -111,11 +111,8 @@ KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
     }
     MKKV_CK(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, dev_));
     MKKV_CK(preload_kernels());
-    // MK_KV_ATTN: "tc" (default: tensor-core kernel, the others as fallbacks), "fast" (no tcgen05 kernel), "baseline" (the simple kernel only)
-    if (const char * c = getenv("MK_KV_ATTN")) {
-        use_fast_ = strcmp(c, "baseline") != 0;
-        use_tc_ = strcmp(c, "baseline") != 0 && strcmp(c, "fast") != 0;
-    }
+    // MK_KV_ATTN: "tc" (default: the tcgen05 kernel, the mma.sync kernel as its fallback) or "fast" (the mma.sync kernel only)
+    if (const char * c = getenv("MK_KV_ATTN")) use_tc_ = strcmp(c, "fast") != 0;
     ensure_xch(((cfg.ctx + ATT_BUCKET - 1) / ATT_BUCKET + 3) / 4 + 2);
     MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&tc_done_), NKV * sizeof(unsigned)));
     MKKV_CK(cudaMemset(tc_done_, 0, NKV * sizeof(unsigned)));
@@ -143,7 +140,8 @@ void KvEngine::ensure_xch(int nb) {
     xnb_ = nb;
 }
 
-// the decode-attention launches of one call: the tensor-core kernel, the fast one, or the baseline one for shapes those do not take
+// the decode-attention launches of one call: the tensor-core kernel, else the mma.sync one (spread over the grid, or, for shapes
+// that mode does not take, one CTA per (kv head, chunk) item)
 void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items, int max_T) {
     if (use_tc_ && njobs == 1) {
         const cudaError_t e = launch_attend_tc(jobs_host[0], num_sms_, part_, ml_, work_items_, xmax_, xmax_ + (size_t) NKV * ATT_NCH * xnb_ * AR,
@@ -164,7 +162,7 @@ void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items,
         if (e != cudaErrorNotSupported) MKKV_CK(e);
         cudaGetLastError();
     }
-    if (use_fast_) {
+    {
         const cudaError_t e = launch_attend_fast(d_jobs_, jobs_host, njobs, items, max_T, num_sms_, part_, ml_, work_items_, xmax_,
                                                  std::min(xnb_, 64), ++epoch_, d_status_, njobs == 1 ? prof_ : nullptr, true, stream_);
         if (e == cudaSuccess) {
@@ -174,7 +172,8 @@ void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items,
         if (e != cudaErrorNotSupported && e != cudaErrorCooperativeLaunchTooLarge) MKKV_CK(e);
         cudaGetLastError();
     }
-    MKKV_CK(launch_attend(d_jobs_, jobs_host, njobs, items, max_T, part_, ml_, d_status_, stream_));
+    MKKV_CK(launch_attend_fast(d_jobs_, jobs_host, njobs, items, max_T, num_sms_, part_, ml_, work_items_, nullptr, 0, 0, d_status_, nullptr,
+                               false, stream_));
     launches_ += 2;
 }
 
@@ -369,7 +368,7 @@ void KvEngine::drop_checkpoints(Seq & s, int after) {
 void KvEngine::reset(int seq) {
     Seq & s = seq_ref(seq);
     s.n = s.kv_top = 0;
-    std::fill(s.spilled.begin(), s.spilled.end(), 0);
+    std::fill(s.spilled.begin(), s.spilled.end(), s.base); // (a split sequence keeps its base: no main row below it exists)
     drop_checkpoints(s, -1);
     s.failed = false;
 }
@@ -470,14 +469,25 @@ void KvEngine::reserve_batch(int njobs) {
     ensure_work(std::max(njobs * NKV * ATT_NCH, num_sms_), njobs);
 }
 
-void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O) {
-    use_device();
-    check_layer(layer);
-    Seq & s = seq_ref(seq);
-    if (T < 1 || T > MAXT) throw std::runtime_error("attend: T must be 1.." + std::to_string(MAXT));
-    if (n < 0 || n + T > s.kv_top) throw std::runtime_error("attend: rows up to " + std::to_string(n + T) + " have not been appended (" + std::to_string(s.kv_top) + " written)");
-    if (!Q || !O) throw std::runtime_error("attend: null Q / O");
-    wait_copies(s);
+// a call that needs the whole sequence on this GPU: not for a sequence whose rows start at a non-zero base (mk_kv_set_base)
+void KvEngine::need_whole(const Seq & s, const char * what) const {
+    if (s.base != 0)
+        throw std::runtime_error(std::string(what) + ": not available on a sequence split by position (its rows start at position " +
+                                 std::to_string(s.base) + "); use attend_partial / combine");
+}
+
+// The job of T query tokens at n over the whole context of one (sequence, layer), after the checks every attention entry shares:
+// the rows exist; the T rows share one partition, i.e. n + 1 .. n + T do not cross a multiple of 640 (the reference's host rule,
+// mk_shared.cuh:288-291: results are independent of T only then); the window's rows are still in the ring.
+AttnJob KvEngine::whole_job(const Seq & s, const char * what, int layer, int n, int T, const void * Q, void * O) const {
+    const std::string w(what);
+    need_whole(s, what);
+    if (T < 1 || T > MAXT) throw std::runtime_error(w + ": T must be 1.." + std::to_string(MAXT));
+    if (n < 0 || n + T > s.kv_top) throw std::runtime_error(w + ": rows up to " + std::to_string(n + T) + " have not been appended (" + std::to_string(s.kv_top) + " written)");
+    if (att_cap_T(n, T) < T)
+        throw std::runtime_error(w + ": " + std::to_string(T) + " tokens at position " + std::to_string(n) + " cross a multiple of " + std::to_string(ATT_BUCKET) +
+                                 " (at most " + std::to_string(att_cap_T(n, T)) + " share one partition: mk_kv_cap_T)");
+    if (!Q || !O) throw std::runtime_error(w + ": null Q / O");
     AttnJob j;
     j.kv = s.views[layer];
     j.Q = static_cast<const uint16_t *>(Q);
@@ -490,6 +500,20 @@ void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O
     j.pos_lo = 0;
     j.pos_hi = n + T;
     j.pstride = 1;
+    // positions >= ws are read from the ring, which holds the newest rc rows written: an attend at an earlier n after rows far
+    // beyond it were appended would read later positions' rows
+    if (rc_ > 0 && (j.kv.s[0].rval || j.kv.s[1].rval) && s.kv_top > j.ws + rc_)
+        throw std::runtime_error(w + ": the window rows of a call at position " + std::to_string(n) + " were overwritten (rows up to " +
+                                 std::to_string(s.kv_top) + " written); truncate first");
+    return j;
+}
+
+void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O) {
+    use_device();
+    check_layer(layer);
+    Seq & s = seq_ref(seq);
+    const AttnJob j = whole_job(s, "attend", layer, n, T, Q, O);
+    wait_copies(s);
     spill_to(s, layer, j.ws); // positions that left the window are read in the main format from now on
     launch_attention(&j, 1, NKV * j.nch, T);
 }
@@ -514,10 +538,11 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
     if (T < 1 || T > MAXT) throw std::runtime_error("attend_partial: T must be 1.." + std::to_string(MAXT));
     if (!Q || !part_out || !ml_out) throw std::runtime_error("attend_partial: null argument");
     const int L = n + T;
+    if (n < 0 || att_cap_T(n, T) < T)
+        throw std::runtime_error("attend_partial: " + std::to_string(T) + " tokens at position " + std::to_string(n) + " cross a multiple of " + std::to_string(ATT_BUCKET));
     if (pos_hi != pos_lo && (pos_lo % ATP || pos_lo < s.base || pos_hi > L || pos_hi < pos_lo || (pos_hi != L && pos_hi % ATP)))
         throw std::runtime_error("attend_partial: bad position range [" + std::to_string(pos_lo) + ", " + std::to_string(pos_hi) + ")");
     if (pos_hi > pos_lo && pos_hi > s.kv_top) throw std::runtime_error("attend_partial: rows up to " + std::to_string(pos_hi) + " have not been appended (" + std::to_string(s.kv_top) + " written)");
-    if (!use_fast_) throw std::runtime_error("attend_partial needs the fast attention kernel (MK_KV_ATTN=baseline is set)");
     wait_copies(s);
     AttnJob j;
     j.kv = s.views[layer];
@@ -602,23 +627,10 @@ void KvEngine::attend_static(int seq, int layer, int n, int T, const void * Q, v
     check_layer(layer);
     Seq & s = seq_ref(seq);
     if (T < 1 || T > MAXT) throw std::runtime_error("attend_static: T must be 1.." + std::to_string(MAXT) + " (the fixed scratch holds " + std::to_string(AR) + " query rows per item)");
-    if (n < 0 || n + T > s.kv_top) throw std::runtime_error("attend_static: rows up to " + std::to_string(n + T) + " have not been appended (" + std::to_string(s.kv_top) + " written)");
-    if (!Q || !O) throw std::runtime_error("attend_static: null Q / O");
-    wait_copies(s);
-    AttnJob j;
-    j.kv = s.views[layer];
-    j.Q = static_cast<const uint16_t *>(Q);
-    j.O = static_cast<float *>(O);
-    j.n = n;
-    j.T = T;
-    attn_dims(n + T, j.nch, j.cs);
-    j.ws = kv_ws(n + T, cfg_.win);
-    j.item0 = 0;
-    j.pos_lo = 0;
-    j.pos_hi = n + T;
-    j.pstride = 1;
+    const AttnJob j = whole_job(s, "attend_static", layer, n, T, Q, O);
     if (NKV * j.nch > STATIC_ITEMS)
         throw std::runtime_error("attend_static: the call needs " + std::to_string(NKV * j.nch) + " partial items, the fixed scratch holds " + std::to_string(STATIC_ITEMS));
+    wait_copies(s);
     spill_to(s, layer, j.ws);
     MKKV_CK(launch_attend_static(j, d_status_, stream_));
     launches_ += 2;
@@ -641,20 +653,15 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
             if (seqs[k] == seqs[j]) throw std::runtime_error("step_batch: sequence listed twice");
         if (T[j] < 1 || T[j] > MAXT) throw std::runtime_error("step_batch: T must be 1.." + std::to_string(MAXT));
         if (n[j] < 0 || n[j] + T[j] > (do_append ? s.ctx : s.kv_top)) throw std::runtime_error("step_batch: rows out of range for job " + std::to_string(j));
+        need_whole(s, "step_batch");
+        // a side request keeps the main sequence's rows aside lazily: they are copied out before this call overwrites them
+        if (do_append && seqs[j] == SEQ_MAIN && sw_on_) sw_need(n[j] + T[j]);
         wait_copies(s);
         if (do_append && cfg_.spill && rc_ > 0) spill_to(s, layer, n[j] + T[j] - rc_);
+        if (do_append) s.kv_top = std::max(s.kv_top, n[j] + T[j]);
         AttnJob & a = h_jobs_[j];
-        a.kv = s.views[layer];
-        a.Q = static_cast<const uint16_t *>(Q) + row * NH * HD;
-        a.O = static_cast<float *>(O) + row * NH * HD;
-        a.n = n[j];
-        a.T = T[j];
-        attn_dims(n[j] + T[j], a.nch, a.cs);
-        a.ws = kv_ws(n[j] + T[j], cfg_.win);
+        a = whole_job(s, "step_batch", layer, n[j], T[j], static_cast<const uint16_t *>(Q) + row * NH * HD, static_cast<float *>(O) + row * NH * HD);
         a.item0 = items;
-        a.pos_lo = 0;
-        a.pos_hi = n[j] + T[j];
-        a.pstride = 1;
         items += NKV * a.nch;
         maxT = std::max(maxT, T[j]);
         aj[j].kv = a.kv;
@@ -664,7 +671,6 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
         aj[j].n = T[j];
         row += T[j];
         spill_to(s, layer, a.ws);
-        if (do_append) s.kv_top = std::max(s.kv_top, n[j] + T[j]);
     }
     if (items > work_items_) throw std::runtime_error("step_batch: call reserve_batch first");
     if (do_append) {
@@ -682,7 +688,7 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
 // ring rows of positions that the abandoned continuation overwrote are rebuilt from the main rows (ck_pool.cu:285-296)
 void KvEngine::ring_rewind(Seq & s, int P) {
     if (cfg_.win > 0) {
-        const int p0 = std::max(0, P - rc_), p1 = std::min(P, s.kv_top - rc_);
+        const int p0 = std::max(s.base, P - rc_), p1 = std::min(P, s.kv_top - rc_); // (a split sequence holds no rows below its base)
         if (p1 > p0) MKKV_CK(launch_refill(s.d_views, cfg_.layers, p0, p1, stream_));
     }
     s.kv_top = std::min(s.kv_top, P);
@@ -692,6 +698,7 @@ void KvEngine::ring_rewind(Seq & s, int P) {
 void KvEngine::truncate(int seq, int len) {
     use_device();
     Seq & s = seq_ref(seq);
+    if (s.base != 0 && len != 0) need_whole(s, "truncate");
     if (len < 0 || len > s.n) throw std::runtime_error("truncate: length " + std::to_string(len) + " not inside the sequence (" + std::to_string(s.n) + ")");
     wait_copies(s);
     ring_rewind(s, len);
@@ -709,6 +716,7 @@ size_t KvEngine::ring_state_bytes() const {
 int KvEngine::checkpoint(int seq) {
     use_device();
     Seq & s = seq_ref(seq);
+    need_whole(s, "checkpoint");
     const int pos = s.n;
     for (auto & k : s.cks)
         if (k.pos == pos) return pos;
@@ -747,6 +755,7 @@ std::vector<int> KvEngine::checkpoints(int seq) const {
 bool KvEngine::rewind_to(int seq, int pos) {
     use_device();
     Seq & s = seq_ref(seq);
+    need_whole(s, "rewind_to");
     const Checkpoint * ck = nullptr;
     for (const auto & k : s.cks)
         if (k.pos == pos && pos >= 0) ck = &k;
@@ -764,6 +773,11 @@ bool KvEngine::rewind_to(int seq, int pos) {
     s.n = pos;
     drop_checkpoints(s, pos);
     return true;
+}
+
+bool KvEngine::rewind_to_checkpoint(int seq) { // the last one (qwen38_mk.h:97-101)
+    const Seq & s = seq_ref(seq);
+    return !s.cks.empty() && rewind_to(seq, s.cks.back().pos);
 }
 
 // ---- host store ----
@@ -837,6 +851,8 @@ KvEngine::StoreInfo KvEngine::store_info() const {
     i.last_ms = hs_ms_;
     i.last_bytes = hs_bytes_;
     i.side_ms = sw_ms_;
+    i.side_park_bytes = sw_park_bytes_;
+    i.side_park_ms = sw_park_ms_;
     return i;
 }
 void KvEngine::kv_sizes(size_t * per_token, size_t * rings, size_t * state, size_t * checkpoint) const {
@@ -904,6 +920,7 @@ int KvEngine::park_len(int id) const {
 int KvEngine::park(int seq, int max_checkpoints, bool wait) {
     use_device();
     Seq & s = seq_ref(seq);
+    need_whole(s, "park");
     if (s.n == 0) return 0;
     const auto t0 = std::chrono::steady_clock::now();
     // spill mode: every position of the sequence gets its main-format row first, so the entry is the reference's byte
@@ -962,10 +979,19 @@ bool KvEngine::unpark(int seq, int id, bool wait) {
     const auto it = parked_.find(id);
     if (it == parked_.end()) return false;
     Seq & s = seq_ref(seq);
+    need_whole(s, "unpark");
+    if (it->second.n > s.ctx) throw std::runtime_error("unpark: the parked conversation (" + std::to_string(it->second.n) + " positions) does not fit the sequence's context");
+    if (seq == SEQ_MAIN && sw_on_) throw std::runtime_error("unpark: a side request is active (side_unpark continues a parked conversation inside it)");
+    (void) wait;
+    unpark_into(s, seq, id);
+    return true;
+}
+
+// the sequence becomes parked entry id (which is freed): rows, rings, checkpoints (host_store.cu:457-483)
+void KvEngine::unpark_into(Seq & s, int seq, int id) {
+    const auto it = parked_.find(id);
     Parked & e = it->second;
-    if (e.n > s.ctx) throw std::runtime_error("unpark: the parked conversation (" + std::to_string(e.n) + " positions) does not fit the sequence's context");
     const auto t0 = std::chrono::steady_clock::now();
-    if (seq == SEQ_MAIN && sw_on_) throw std::runtime_error("unpark: a side request is active");
     reset(seq);
     // the side stream starts after the compute stream's pending work on this sequence
     MKKV_CK(cudaEventRecord(ev_compute_, stream_));
@@ -996,9 +1022,7 @@ bool KvEngine::unpark(int seq, int id, bool wait) {
     hs_bytes_ = e.blob.used;
     hs_release(e.blob);
     parked_.erase(it);
-    (void) wait;
     hs_ms_ = ms_since(t0);
-    return true;
 }
 
 // Rows [0, P) of a parked conversation into the sequence, leaving the entry parked: the main rows of every region come
@@ -1009,6 +1033,7 @@ bool KvEngine::restore_prefix(int seq, int id, int P, bool wait) {
     const auto it = parked_.find(id);
     if (it == parked_.end()) return false;
     Seq & s = seq_ref(seq);
+    need_whole(s, "restore_prefix");
     const Parked & e = it->second;
     if (P < 0 || P > e.n || P > s.ctx) throw std::runtime_error("restore_prefix: position " + std::to_string(P) + " outside the parked conversation");
     const auto t0 = std::chrono::steady_clock::now();
@@ -1059,6 +1084,7 @@ bool KvEngine::side_begin() {
     if (sw_on_) throw std::runtime_error("side_begin: a side request is already active");
     if (hs_budget_ == 0) return false;
     Seq & s = main_;
+    need_whole(s, "side_begin");
     for (int l = 0; l < cfg_.layers; l++) spill_to(s, l, s.n); // (the shadow rows will be overwritten: make the main rows now)
     sw_on_ = true;
     sw_broken_ = false;
@@ -1136,6 +1162,59 @@ int KvEngine::side_end() {
     return 1;
 }
 
+// side_end with the side request's own conversation parked first (host_store.cu:371-396). *id: its entry, 0 when it is empty
+// or the store has no room. 1: the kept sequence is back; 0: it was lost (the store ran full during the side request): the side
+// request's conversation stays as the engine's sequence.
+int KvEngine::side_end_park(int max_checkpoints, int * id) {
+    use_device();
+    if (!sw_on_) throw std::runtime_error("side_end_park: no side request");
+    *id = 0;
+    sw_park_bytes_ = 0;
+    sw_park_ms_ = 0;
+    const auto t0 = std::chrono::steady_clock::now();
+    const int pid = park(SEQ_MAIN, max_checkpoints, true);
+    if (pid > 0) {
+        *id = pid;
+        sw_park_bytes_ = park_bytes(pid);
+        sw_park_ms_ = ms_since(t0);
+    }
+    if (sw_broken_) { // nothing to bring back: drop what was kept, leave the side request's conversation in place
+        MKKV_CK(cudaStreamSynchronize(st_copy_));
+        sw_on_ = false;
+        sw_pieces_.clear();
+        for (auto & k : sw_cks_)
+            if (k.ring) cudaFreeHost(k.ring);
+        sw_cks_.clear();
+        hs_release(sw_blob_);
+        return 0;
+    }
+    return side_end();
+}
+
+// Right after side_begin: the side request continues parked conversation id (the engine becomes it, the entry is freed) while
+// the kept sequence stays aside: the rows and rings it overwrites go to the store first (host_store.cu:398-455).
+// 1 done, 0 no room in the store (nothing changed), -1 no such entry.
+int KvEngine::side_unpark(int id) {
+    use_device();
+    if (!sw_on_) throw std::runtime_error("side_unpark: no side request");
+    const auto it = parked_.find(id);
+    if (it == parked_.end()) return -1;
+    Seq & s = main_;
+    if (s.n != 0 || s.kv_top != 0) throw std::runtime_error("side_unpark: only right after side_begin");
+    const int n = it->second.n;
+    if (n > s.ctx) throw std::runtime_error("side_unpark: the parked conversation (" + std::to_string(n) + " positions) does not fit the context");
+    if (sw_broken_) return 0;
+    // the copy-out sw_need(n) would make, checked for room first so that a full store changes nothing
+    constexpr int SW_BLK = 1024;
+    const int up = (n + MAXT + SW_BLK - 1) / SW_BLK * SW_BLK, want = std::max(sw_hi_, std::min(sw_top_, up));
+    const bool rings = !sw_rings_saved_ && rc_ > 0;
+    if (!blob_room(sw_blob_, stream_bytes(s, sw_hi_, want, 0, rings ? rc_ : 0))) return 0;
+    sw_need(n);
+    if (sw_broken_) return 0;
+    unpark_into(s, SEQ_MAIN, id);
+    return 1;
+}
+
 void KvEngine::side_drop() {
     use_device();
     MKKV_CK(cudaStreamSynchronize(st_copy_));
@@ -1169,6 +1248,7 @@ static unsigned long long dg_hash(const void * p, size_t nb, unsigned long long 
 std::vector<unsigned long long> KvEngine::state_digest(int seq) {
     use_device();
     Seq & s = seq_ref(seq);
+    need_whole(s, "state_digest");
     sync();
     typedef unsigned long long u64;
     const int n = s.n, rc = cfg_.win > 0 ? rc_ : 0, rlo = rc ? std::max(0, n - rc) : n;

@@ -97,6 +97,7 @@ class KvEngine {
     int checkpoint(int seq);              // saves a checkpoint at the committed position; returns it
     std::vector<int> checkpoints(int seq) const;
     bool rewind_to(int seq, int pos);     // engine.cu:1197-1204, ck_pool.cu:268-296
+    bool rewind_to_checkpoint(int seq);   // to the last checkpoint; false: none
 
     // ---- host store ----
     void store_budget(size_t bytes);
@@ -107,6 +108,8 @@ class KvEngine {
         double last_ms = 0;
         size_t last_bytes = 0;
         double side_ms = 0;
+        size_t side_park_bytes = 0; // the last side_end_park: its park of the side request's conversation (0: not parked)
+        double side_park_ms = 0;
     };
     StoreInfo store_info() const;
     void kv_sizes(size_t * per_token, size_t * rings, size_t * state, size_t * checkpoint) const;
@@ -120,6 +123,8 @@ class KvEngine {
     void store_wait(); // completion of the copies enqueued by park / unpark / restore_prefix with wait = false
     bool side_begin();
     int side_end();
+    int side_end_park(int max_checkpoints, int * id); // host_store.cu:371-396
+    int side_unpark(int id);                          // host_store.cu:398-455
     void side_drop();
     bool side_active() const { return sw_on_; }
 
@@ -168,6 +173,9 @@ class KvEngine {
     void free_seq(Seq & s);
     void use_device() const;
     void check_layer(int layer) const;
+    void need_whole(const Seq & s, const char * what) const;
+    AttnJob whole_job(const Seq & s, const char * what, int layer, int n, int T, const void * Q, void * O) const;
+    void unpark_into(Seq & s, int seq, int id);
     void spill_to(Seq & s, int layer, int upto);
     void ring_rewind(Seq & s, int P);
     void drop_checkpoints(Seq & s, int after);
@@ -216,7 +224,7 @@ class KvEngine {
     // fast attention path: exchange of row maxima between the CTAs of one chunk
     unsigned long long * xmax_ = nullptr;
     int epoch_ = 0, num_sms_ = 0;
-    bool use_fast_ = true, use_tc_ = true;
+    bool use_tc_ = true;
     int xnb_ = 0; // batches per chunk the exchange arrays hold
     unsigned * tc_done_ = nullptr; // fused merge of the tensor-core kernel: per kv head, CTAs done over all launches
     unsigned tc_done_seq_ = 0;     // launches that counted on it
@@ -243,7 +251,8 @@ class KvEngine {
     struct SwPiece { int a, b; bool rings; size_t off, bytes; };
     std::vector<SwPiece> sw_pieces_;
     bool sw_rings_saved_ = false;
-    double sw_ms_ = 0;
+    double sw_ms_ = 0, sw_park_ms_ = 0;
+    size_t sw_park_bytes_ = 0;
     void sw_need(int X);
 };
 

@@ -21,20 +21,15 @@ cudaError_t launch_spill(const KvView * views, int layers, int p0, int p1, cudaS
 // ring rows of positions [p0, p1) rebuilt from the main rows (after a rewind), all layers of one sequence
 cudaError_t launch_refill(const KvView * views, int layers, int p0, int p1, cudaStream_t stream);
 
-// split-K decode attention over the (kv head, chunk) items of njobs jobs, then the merge. jobs: device array (njobs > 1)
-// or null with the single job passed by value. part: [items][48][256] fp32, ml: [items][48] (m, l). status: device-visible word.
-cudaError_t launch_attend(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
-                          float2 * ml, int * status, cudaStream_t stream);
-
 // the merge alone: job j's partials are slots item0 + g nch .. + nch - 1 of kv head g
 // raw_part / raw_ml (one job only): write the merged but un-normalised result as one partial per kv head, [4][48][256] floats and
 // [4][48] (m, l), instead of the job's O
 cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,
                          cudaStream_t stream, float * raw_part = nullptr, float2 * raw_ml = nullptr);
-// Fast path (kv_attend_fast.cu): same result as launch_attend. One job: cooperative launch over num_sms CTAs with an
+// mma.sync path (kv_attend_fast.cu). One job: cooperative launch over num_sms CTAs with an
 // exchange of row maxima through xmax ([4][20][nbmax][48] 8-byte words {epoch, value}, zeroed once; epoch must be non-zero and
 // differ from every earlier launch's). Several jobs: one CTA per (job, kv head, chunk). part / ml hold part_slots partials.
-// cudaErrorNotSupported: shape not handled (use launch_attend).
+// cudaErrorNotSupported: shape not handled (one job spread over the grid only: the one-CTA-per-item mode takes every shape).
 cudaError_t launch_attend_fast(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, int num_sms,
                                float * part, float2 * ml, int part_slots, unsigned long long * xmax, int nbmax, int epoch, int * status,
                                unsigned long long * prof, bool spread, cudaStream_t stream, const AttnTask * tasks_dev = nullptr,
@@ -67,6 +62,10 @@ size_t attend_tc_smem_bytes();
 cudaError_t preload_kernels();
 cudaError_t preload_attend_fast();
 cudaError_t preload_attend_tc();
+// Wait limits of the tensor-core kernel's launches that follow (process-wide; for diagnostics and the failure-path test): a failed
+// mbarrier try suspends for up to hint_ns, `rounds` failed tries or `polls` failed polls of an exchange word make a CTA give up.
+void attend_tc_set_wait_limits(unsigned hint_ns, unsigned rounds, unsigned polls);
+void attend_tc_default_wait_limits();
 
 // batched append: job j writes n rows at pos0 of its own (sequence, layer)
 struct AppendJob {
@@ -90,13 +89,12 @@ constexpr int MAX_REGIONS = MAX_LAYERS * 2 * NKV * 2 * 2;
 cudaError_t launch_gather(const CopyRegion * regions, int nregions, int a, int b, int ra, int rb, unsigned long long off,
                           unsigned long long len, uint8_t * staging, bool scatter, cudaStream_t stream);
 
-size_t attend_smem_bytes();
 
 // Decode attention of ONE job whose split partials live in a fixed array inside the library's device image instead of
 // memory obtained from the CUDA allocator. The array holds STATIC_ITEMS (kv head, chunk) items: enough for any single
 // job (the partition never makes more than NKV * ATT_NCH), about 3.96 MB per GPU that loads the library, held until the
-// process exits. The first call on a device looks the array's device address up (cudaGetSymbolAddress); make that call
-// outside stream capture. Returns cudaErrorInvalidValue if the job needs more items than the array holds.
+// process exits. The array's device address is looked up (cudaGetSymbolAddress) by preload_kernels, which every engine runs at
+// construction. Returns cudaErrorInvalidValue if the job needs more items than the array holds.
 constexpr int STATIC_ITEMS = NKV * ATT_NCH;
 cudaError_t launch_attend_static(const AttnJob & job, int * status, cudaStream_t stream);
 

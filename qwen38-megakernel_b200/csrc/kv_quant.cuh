@@ -1,6 +1,13 @@
-// Device-side quantizer of one K / V row, one warp per row: lane l holds values 8 l .. 8 l + 7, a 32-value block is lanes
-// 4 j .. 4 j + 3. Bytes and rounding follow the reference exactly (qwen38_mk.cu:2003-2097): every fp32 operation below is
-// an explicitly rounded intrinsic so no compiler flag can change a stored byte.
+// Device-side quantizer of one K / V row, one warp per row: lane l holds values 8 l .. 8 l + 7, a 32-value block is the four
+// lanes of a quad (lanes 4 j .. 4 j + 3). The stored bytes are the reference's (qwen38_mk.cu:2003-2097) bit for bit; the
+// golden vectors under tests/golden/ pin them. What the format fixes is the fp32 arithmetic of the scale and of the index
+// (every such operation below is an explicitly rounded intrinsic, so no compiler flag can change a byte) and the byte layout;
+// how the block's extreme value is found and how the bytes are assembled is this file's own:
+//   - magnitudes are compared as the integer bit patterns of |v| (same order as the floats for finite values) and reduced over
+//     the quad with one redux.sync;
+//   - the signed extreme of a 4 .. 7-bit block ("largest magnitude, ties to the larger value") is +max if any value of the block
+//     equals +max, else -max, found with one quad vote;
+//   - indices are packed four to a word with byte permutes, nibbles and high-bit fields are cut out of those words.
 #pragma once
 #include <cuda_fp16.h>
 
@@ -10,46 +17,57 @@ namespace mkkv {
 
 constexpr unsigned FULL = 0xffffffffu;
 
-// 256-point Walsh-Hadamard transform x 1/16 (orthonormal, self-inverse): the in-lane index bits first, then the lane
-// bits, the same butterfly order as qwen38_mk.cu:2049-2069 (fp32 sums do not commute in rounding)
+// the lanes of this lane's quad, as a member mask
+__device__ __forceinline__ unsigned quad_mask(int lane) { return 0xfu << (lane & 28); }
+
+// 256-point Walsh-Hadamard transform x 1/16 (orthonormal, self-inverse). fp32 sums do not commute in rounding, so the stage
+// order is the format's (qwen38_mk.cu:2049-2069): index bits 1, 2, 4 inside the lane, then lane bits 1 .. 16; in every stage the
+// element whose bit is clear becomes a + b, the other a - b with a the clear-bit element. Across lanes that is
+// partner + own for a clear lane bit and partner - own = partner + (-own) for a set one: one add of a sign-adjusted value.
 __device__ __forceinline__ void fwht256(float (&v)[8], int lane) {
 #pragma unroll
-    for (int m = 1; m < 8; m <<= 1)
+    for (int stride = 1; stride < 8; stride *= 2)
 #pragma unroll
-        for (int k = 0; k < 8; k++)
-            if (!(k & m)) {
-                const float a = v[k], b = v[k | m];
-                v[k] = __fadd_rn(a, b);
-                v[k | m] = __fsub_rn(a, b);
+        for (int base = 0; base < 8; base += 2 * stride)
+#pragma unroll
+            for (int j = base; j < base + stride; j++) {
+                const float lo = v[j], hi = v[j + stride];
+                v[j] = __fadd_rn(lo, hi);
+                v[j + stride] = __fsub_rn(lo, hi);
             }
 #pragma unroll
-    for (int m = 1; m < 32; m <<= 1)
+    for (int bit = 1; bit < 32; bit *= 2) {
+        const unsigned flip = (lane & bit) ? 0x80000000u : 0u; // own value enters negated where the lane bit is set
 #pragma unroll
         for (int k = 0; k < 8; k++) {
-            const float o = __shfl_xor_sync(FULL, v[k], m);
-            v[k] = (lane & m) ? __fsub_rn(o, v[k]) : __fadd_rn(v[k], o);
+            const float partner = __shfl_xor_sync(FULL, v[k], bit);
+            v[k] = __fadd_rn(partner, __uint_as_float(__float_as_uint(v[k]) ^ flip));
         }
+    }
 #pragma unroll
     for (int k = 0; k < 8; k++) v[k] = __fmul_rn(v[k], 0.0625f);
 }
 
+// bit pattern of the block's largest magnitude (the block: this lane's quad)
+__device__ __forceinline__ unsigned block_absmax_bits(const float (&v)[8], int lane) {
+    unsigned m = 0u;
+#pragma unroll
+    for (int k = 0; k < 8; k++) m = max(m, __float_as_uint(v[k]) & 0x7fffffffu);
+    return __reduce_max_sync(quad_mask(lane), m);
+}
+// four small non-negative integers (each < 256) as the bytes of one word, a in the lowest
+__device__ __forceinline__ unsigned bytes4(int a, int b, int c, int d) {
+    return __byte_perm(__byte_perm((unsigned) a, (unsigned) b, 0x0040), __byte_perm((unsigned) c, (unsigned) d, 0x0040), 0x5410);
+}
+
 // q8_0 row (qwen38_mk.cu:2005-2023): q = rint(v * (127 / absmax)) to even, scale = half(absmax / 127)
 __device__ __forceinline__ void store_q8(uint8_t * q, uint16_t * sc, const float (&v)[8], int lane) {
-    float am = 0.f;
+    const float am = __uint_as_float(block_absmax_bits(v, lane));
+    const float inv = am > 0.f ? __fdiv_rn(127.0f, am) : 0.f;
+    int n[8];
 #pragma unroll
-    for (int k = 0; k < 8; k++) am = fmaxf(am, fabsf(v[k]));
-    am = fmaxf(am, __shfl_xor_sync(FULL, am, 1));
-    am = fmaxf(am, __shfl_xor_sync(FULL, am, 2));
-    const float id = am > 0.f ? __fdiv_rn(127.0f, am) : 0.f;
-    unsigned w[2];
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-        unsigned x = 0;
-#pragma unroll
-        for (int k = 0; k < 4; k++) x |= ((unsigned) __float2int_rn(__fmul_rn(v[4 * h + k], id)) & 0xffu) << (8 * k);
-        w[h] = x;
-    }
-    *reinterpret_cast<uint2 *>(q + lane * 8) = make_uint2(w[0], w[1]);
+    for (int k = 0; k < 8; k++) n[k] = __float2int_rn(__fmul_rn(v[k], inv)) & 0xff; // two's-complement byte
+    *reinterpret_cast<uint2 *>(q + lane * 8) = make_uint2(bytes4(n[0], n[1], n[2], n[3]), bytes4(n[4], n[5], n[6], n[7]));
     if ((lane & 3) == 0) sc[lane >> 2] = __half_as_ushort(__float2half_rn(__fdiv_rn(am, 127.0f)));
 }
 
@@ -57,27 +75,29 @@ __device__ __forceinline__ void store_q8(uint8_t * q, uint16_t * sc, const float
 // index n = min(2^bits - 1, trunc(fma(v, 1 / d, 2^(bits-1) + 0.5))). Bytes 0 .. 127: lane word of low nibbles (values 0 .. 3 in the
 // low, 4 .. 7 in the high nibbles of bytes 0 .. 3); then bits - 4 bytes per lane of high bits, value k at bit (bits - 4) k.
 __device__ __forceinline__ void store_qn(uint8_t * q, uint16_t * sc, const float (&v)[8], int bits, int lane) {
-    const int h = 1 << (bits - 1), hb = bits - 4;
-    float am = 0.f, sv = 0.f;
+    const int half_range = 1 << (bits - 1), hb = bits - 4;
+    const unsigned am_bits = block_absmax_bits(v, lane);
+    bool has_pos = false; // does the block hold +max itself?
 #pragma unroll
-    for (int k = 0; k < 8; k++)
-        if (fabsf(v[k]) > am || (fabsf(v[k]) == am && v[k] > sv)) { am = fabsf(v[k]); sv = v[k]; }
+    for (int k = 0; k < 8; k++) has_pos |= __float_as_uint(v[k]) == am_bits;
+    const bool any_pos = (__ballot_sync(FULL, has_pos) & quad_mask(lane)) != 0u;
+    // an all-zero block keeps the search's initial +0 whatever the zeros' signs, so its scale is -0 (+0 / -2^(bits-1))
+    const float extreme = __uint_as_float(am_bits == 0u || any_pos ? am_bits : am_bits | 0x80000000u);
+    const float d = __fdiv_rn(extreme, (float) -half_range), inv = d != 0.f ? __fdiv_rn(1.0f, d) : 0.f;
+    const float offset = (float) half_range + 0.5f;
+    int n[8];
 #pragma unroll
-    for (int m = 1; m <= 2; m <<= 1) {
-        const float oa = __shfl_xor_sync(FULL, am, m), os = __shfl_xor_sync(FULL, sv, m);
-        if (oa > am || (oa == am && os > sv)) { am = oa; sv = os; }
+    for (int k = 0; k < 8; k++) n[k] = min(2 * half_range - 1, (int) __fmaf_rn(v[k], inv, offset));
+    const unsigned first = bytes4(n[0], n[1], n[2], n[3]), second = bytes4(n[4], n[5], n[6], n[7]); // one index per byte
+    *reinterpret_cast<unsigned *>(q + lane * 4) = (first & 0x0f0f0f0fu) | ((second & 0x0f0f0f0fu) << 4);
+    if (hb > 0) {
+        const unsigned top[2] = {(first >> 4) & 0x0f0f0f0fu, (second >> 4) & 0x0f0f0f0fu}; // the indices' bits 4 and up, one per byte
+        unsigned field = 0u;
+#pragma unroll
+        for (int k = 0; k < 8; k++) field |= ((top[k >> 2] >> (8 * (k & 3))) & 0xfu) << (hb * k);
+        uint8_t * dst = q + 128 + lane * hb;
+        for (int b = 0; b < hb; b++) dst[b] = (uint8_t) (field >> (8 * b));
     }
-    const float d = __fdiv_rn(sv, (float) -h), id = d != 0.f ? __fdiv_rn(1.0f, d) : 0.f;
-    const float c = (float) h + 0.5f;
-    unsigned lo = 0, hi = 0;
-#pragma unroll
-    for (int k = 0; k < 8; k++) {
-        const unsigned n = (unsigned) min(2 * h - 1, (int) __fmaf_rn(v[k], id, c));
-        lo |= (n & 15u) << (k < 4 ? 8 * k : 8 * (k - 4) + 4);
-        hi |= (n >> 4) << (hb * k);
-    }
-    *reinterpret_cast<unsigned *>(q + lane * 4) = lo;
-    for (int k = 0; k < hb; k++) q[128 + lane * hb + k] = (uint8_t) ((hi >> (8 * k)) & 0xffu);
     if ((lane & 3) == 0) sc[lane >> 2] = __half_as_ushort(__float2half_rn(d));
 }
 
@@ -100,8 +120,10 @@ __device__ __forceinline__ void row_ints(const uint8_t * row, int bits, int lane
     for (int k = 0; k < hb; k++) hi |= (unsigned) row[128 + lane * hb + k] << (8 * k);
     const unsigned m = (1u << hb) - 1u;
 #pragma unroll
-    for (int k = 0; k < 8; k++)
-        q[k] = (int) (((wd >> (k < 4 ? 8 * k : 8 * (k - 4) + 4)) & 0xfu) | (((hi >> (hb * k)) & m) << 4)) - mid;
+    for (int k = 0; k < 8; k++) {
+        const unsigned byte = (wd >> (8 * (k & 3))) & 0xffu, nib = k < 4 ? (byte & 0xfu) : (byte >> 4);
+        q[k] = (int) (nib | (((hi >> (hb * k)) & m) << 4)) - mid;
+    }
 }
 
 } // namespace mkkv

@@ -90,7 +90,7 @@ template <int HB> MKKV_HD unsigned quad_bytes(unsigned word, unsigned hi, int ha
     unsigned x = (word >> (4 * half)) & 0x0f0f0f0fu;
     if constexpr (HB > 0) {
         const unsigned f = hi >> (4 * HB * half), m = (1u << HB) - 1u;
-#if defined(__CUDACC__)
+#if defined(__CUDA_ARCH__)
 #pragma unroll
 #endif
         for (int k = 0; k < 4; k++) x |= ((f >> (HB * k)) & m) << (8 * k + 4);

@@ -44,6 +44,8 @@ def load_library():
         "mk_reset": (None, [vp]),
         "mk_kv_set_stream": (i, [vp, vp]),
         "mk_kv_sync": (i, [vp]),
+        "mk_kv_wait_limits": (i, [C.c_uint, C.c_uint, C.c_uint]),
+        "mk_kv_wait_limits_expire_now": (i, []),
         "mk_kv_append": (i, [vp, i, i, i, i, vp, vp]),
         "mk_kv_attend": (i, [vp, i, i, i, i, vp, vp]),
         "mk_kv_attend_static": (i, [vp, i, i, i, i, vp, vp]),
@@ -65,6 +67,7 @@ def load_library():
         "mk_kv_checkpoints": (i, [vp, i, ip, i]),
         "mk_rewind_to": (i, [vp, i]),
         "mk_kv_rewind_to": (i, [vp, i, i]),
+        "mk_rewind_to_checkpoint": (i, [vp]),
         "mk_store_budget": (i, [vp, ll]),
         "mk_store_reserve": (i, [vp, ll]),
         "mk_store_info": (i, [vp, llp, i]),
@@ -80,9 +83,12 @@ def load_library():
         "mk_kv_store_wait": (i, [vp]),
         "mk_side_begin": (i, [vp]),
         "mk_side_end": (i, [vp]),
+        "mk_side_end_park": (i, [vp, i, ip]),
+        "mk_side_unpark": (i, [vp, i]),
         "mk_side_drop": (i, [vp]),
         "mk_side_active": (i, [vp]),
         "mk_slots_open": (i, [vp, i, i]),
+        "mk_slots_open2": (i, [vp, i, i, i]),
         "mk_slots_count": (i, [vp]),
         "mk_state_digest": (i, [vp, ullp, i]),
         "mk_kv_state_digest": (ll, [vp, i, ullp, ll]),
@@ -166,6 +172,14 @@ class Engine:
     def sync(self):
         self._ck(self.L.mk_kv_sync(self.h), "sync")
 
+    def wait_limits(self, hint_ns=0, rounds=0, polls=0):
+        """limits of the attention kernel's device-side waits for the launches that follow (process-wide); all 0: the defaults"""
+        self.L.mk_kv_wait_limits(hint_ns, rounds, polls)
+
+    def wait_limits_expire_now(self):
+        """the first device-side wait that does not succeed at once gives up (failure-path test)"""
+        self.L.mk_kv_wait_limits_expire_now()
+
     def reset(self):
         self.L.mk_reset(self.h)
 
@@ -248,6 +262,9 @@ class Engine:
     def rewind_to(self, pos, seq=SEQ_MAIN):
         return self.L.mk_kv_rewind_to(self.h, seq, pos) == 0
 
+    def rewind_to_checkpoint(self):
+        return self.L.mk_rewind_to_checkpoint(self.h) == 0
+
     # ---- host store ----
     def store_budget(self, nbytes):
         self._ck(self.L.mk_store_budget(self.h, int(nbytes)), "store_budget")
@@ -298,6 +315,16 @@ class Engine:
 
     def side_end(self):
         return self._ck(self.L.mk_side_end(self.h), "side_end") == 1
+
+    def side_end_park(self, max_cks=0):
+        """(kept sequence is back, id of the side request's parked conversation or 0)"""
+        pid = C.c_int(0)
+        r = self._ck(self.L.mk_side_end_park(self.h, max_cks, C.byref(pid)), "side_end_park")
+        return r == 1, pid.value
+
+    def side_unpark(self, pid):
+        """True: the side request continues parked conversation pid; False: no room in the store (nothing changed)"""
+        return self._ck(self.L.mk_side_unpark(self.h, pid), "side_unpark") == 0
 
     def side_drop(self):
         self._ck(self.L.mk_side_drop(self.h), "side_drop")
