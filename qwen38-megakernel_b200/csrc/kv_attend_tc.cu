@@ -36,6 +36,7 @@
 #include "kv_merge.cuh"
 #include "kv_quant.cuh"
 #include "kv_unpack.h"
+#include "kv_attend_tc_unpack.cuh"
 
 namespace mkkv {
 
@@ -129,6 +130,9 @@ struct Args {
     unsigned wait_hint_ns, wait_rounds, poll_rounds; // limits of the waits: a failed mbarrier try suspends for up to wait_hint_ns,
                                                      // wait_rounds failed tries (poll_rounds failed polls of an exchange word) give up
 };
+#ifndef MKKV_ABL
+#define MKKV_ABL 0 // experiments only (wrong results): 1 no unpack arithmetic, 2 no P arithmetic, 4 no tile maxima
+#endif
 #ifndef MKKV_TC_PROF
 #define MKKV_TC_PROF 0 // 1: compile the phase stamps in (they cost a few per cent)
 #endif
@@ -245,122 +249,6 @@ __device__ __forceinline__ float exp_neg(float x) {
 #endif
 }
 
-// ---- one worker step: position `row` of a staged tile, dims 32 jb .. 32 jb + 31 -> four 16-byte operand units ----
-// A unit holds the 8 values of one lane word in the order UNIT_PERM (kv_unpack.h: pair_words and friends are the host-checkable
-// statement of what follows). The instructions are chosen by hand -- one AND-OR per pair for the high bits under the bias, one for
-// the nibbles, a subtract and a multiply in fp16 pairs -- because the compiler re-associates the plain C form into half as many
-// again. raw, dst: shared-space addresses; dst: the thread's unit of dim group 4 (jb & 3) of the slot, the next dim groups are 2048
-// bytes apart. valid false (a row past the chunk end holds stale bytes): zeros.
-__device__ __forceinline__ unsigned and_or(unsigned a, unsigned mask, unsigned c) { // (a & mask) | c
-    unsigned d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
-    return d;
-}
-template <unsigned MASK> __device__ __forceinline__ unsigned and_or_imm(unsigned a, unsigned c) { // (a & MASK) | c, the mask an immediate
-    unsigned d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "n"(MASK), "r"(c));
-    return d;
-}
-// fp16(d * q) of a pair held as (bias + n): the difference is exact, the product is rounded once
-template <unsigned SUB> __device__ __forceinline__ unsigned pair_val(unsigned x, unsigned d) {
-    unsigned r;
-    asm("{\n\t.reg .b32 t;\n\tsub.f16x2 t, %1, %2;\n\tmul.f16x2 %0, t, %3;\n\t}" : "=r"(r) : "r"(x), "r"(SUB), "r"(d));
-    return r;
-}
-__device__ __forceinline__ void sts128(unsigned addr, unsigned a, unsigned b, unsigned c, unsigned d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ uint4 lds128(unsigned addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(unsigned addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned lds32(unsigned addr) {
-    unsigned v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned lds16(unsigned addr) {
-    unsigned short v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
-    return v;
-}
-// one unit: the pairs' high-bit words y0 .. y3 (bias included) and the lane word -> four values, stored
-template <int BITS> __device__ __forceinline__ void unit_out(unsigned dst, unsigned word, unsigned y0, unsigned y1, unsigned y2, unsigned y3, unsigned d) {
-    constexpr unsigned SA = MAGIC_A + (0x00010001u << (BITS - 1)), SB = MAGIC_B + (0x00100010u << (BITS - 1));
-    const unsigned w8 = word >> 8;
-    sts128(dst, pair_val<SA>(and_or_imm<NIB_A>(word, y0), d), pair_val<SB>(and_or_imm<NIB_B>(word, y1), d),
-           pair_val<SA>(and_or_imm<NIB_A>(w8, y2), d), pair_val<SB>(and_or_imm<NIB_B>(w8, y3), d));
-}
-template <int BITS> __device__ __forceinline__ void dq_item(unsigned raw, int row, int jb, bool valid, unsigned dst) {
-    const unsigned sc = valid ? lds16(raw + TILE_SC_OFF + (row * 8 + jb) * 2) : 0u;
-    const unsigned d = sc | (sc << 16);
-    const unsigned rp = raw + row * (32 * BITS);
-    if constexpr (BITS == 8) {
-        const uint4 v0 = lds128(rp + 32 * jb), v1 = lds128(rp + 32 * jb + 16);
-        const unsigned w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        constexpr unsigned S8 = MAGIC_A + 0x00800080u;
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const unsigned lo = w[2 * u] ^ 0x80808080u, hi = w[2 * u + 1] ^ 0x80808080u; // q + 128
-            sts128(dst + u * 2048, pair_val<S8>(__byte_perm(lo, MAGIC_A, 0x7270), d), // (value 0, value 2) under the exponent of 1024
-                   pair_val<S8>(__byte_perm(hi, MAGIC_A, 0x7270), d),                 // (4, 6)
-                   pair_val<S8>(__byte_perm(lo, MAGIC_A, 0x7371), d),                 // (1, 3)
-                   pair_val<S8>(__byte_perm(hi, MAGIC_A, 0x7371), d));                // (5, 7)
-        }
-    } else {
-        const uint4 nv = lds128(rp + 16 * jb);
-        const unsigned nw[4] = {nv.x, nv.y, nv.z, nv.w};
-        if constexpr (BITS == 4) {
-#pragma unroll
-            for (int u = 0; u < 4; u++) unit_out<4>(dst + u * 2048, nw[u], MAGIC_A, MAGIC_B, MAGIC_A, MAGIC_B, d);
-        } else if constexpr (BITS == 5) {
-            const unsigned h = lds32(rp + 128 + 4 * jb);
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                // bit k of the word's byte of high bits at 4 + k and 18 + k; the copy one lower serves the odd values
-                const unsigned hb = __byte_perm(h, 0u, 0x4440 + u), t = hb * 0x00040010u, t1 = hb * 0x00020008u;
-                unit_out<5>(dst + u * 2048, nw[u], and_or_imm<0x00100010u>(t, MAGIC_A), and_or_imm<0x01000100u>(t, MAGIC_B),
-                            and_or_imm<0x00100010u>(t1, MAGIC_A), and_or_imm<0x01000100u>(t1, MAGIC_B), d);
-            }
-        } else if constexpr (BITS == 6) {
-            const uint2 h = lds64(rp + 128 + 8 * jb);
-            const unsigned hw[4] = {h.x, h.x >> 16, h.y, h.y >> 16};
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                // even values' 2-bit fields at bits 0, 4, 8, 12 of he, odd values' of ho: the gaps keep the shifted copies' sums apart
-                const unsigned he = hw[u] & 0x3333u, ho = (hw[u] >> 2) & 0x3333u;
-                unit_out<6>(dst + u * 2048, nw[u], and_or_imm<0x00300030u>(he * 0x00010010u, MAGIC_A), and_or_imm<0x03000300u>(he * 0x00001001u, MAGIC_B),
-                            and_or_imm<0x00300030u>(ho * 0x00010010u, MAGIC_A), and_or_imm<0x03000300u>(ho * 0x00001001u, MAGIC_B), d);
-            }
-        } else { // 7 bits: every pair under the 1024 bias (pair_words7)
-            const unsigned h0 = lds32(rp + 128 + 12 * jb), h1 = lds32(rp + 132 + 12 * jb), h2 = lds32(rp + 136 + 12 * jb);
-            const unsigned hw[4] = {h0, __funnelshift_r(h0, h1, 24), __funnelshift_r(h1, h2, 16), h2 >> 8}; // (bits above 23: not read)
-            constexpr unsigned S7 = MAGIC_A + 0x00400040u;
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                unsigned x[4];
-                pair_words7(nw[u], hw[u], x);
-                sts128(dst + u * 2048, pair_val<S7>(x[0], d), pair_val<S7>(x[1], d), pair_val<S7>(x[2], d), pair_val<S7>(x[3], d));
-            }
-        }
-    }
-}
-__device__ __forceinline__ void dq_item_any(int bits, unsigned raw, int row, int jb, bool valid, unsigned dst) {
-    switch (bits) {
-    case 4: dq_item<4>(raw, row, jb, valid, dst); break;
-    case 5: dq_item<5>(raw, row, jb, valid, dst); break;
-    case 6: dq_item<6>(raw, row, jb, valid, dst); break;
-    case 7: dq_item<7>(raw, row, jb, valid, dst); break;
-    default: dq_item<8>(raw, row, jb, valid, dst); break;
-    }
-}
-
 // max over the warp (sm_100a: redux.sync on fp32)
 __device__ __forceinline__ float warp_max(float x) {
     float r;
@@ -410,7 +298,9 @@ __device__ __forceinline__ Task make_task4(const Geo4 & G4, int t) {
     return k;
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_constant__ Args a) {
+// KB / VB: the bits of the K / V main rows the instance is compiled for (0: any, decided per tile at run time). A compiled-in
+// format leaves two unpack bodies per side (the format and the q8_0 ring) instead of five: a smaller instruction footprint.
+template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_constant__ Args a) {
     // (the dynamic shared memory starts on a 128-byte boundary -- there is no static shared memory in this kernel --, which is all the
     // bulk copies, matrix descriptors and barriers need; no pointer arithmetic here, so every access below is a shared-space one)
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -562,14 +452,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     umma_commit(&sm.s_full[sb]);
                     nk++;
                 } else { // O^T += V^T P^T(nv), P as its high and low parts
+#if MKKV_TC_PROF == 1
                     TC_STAMP(nv, 16);
+#endif
                     tc_wait(&sm.p_full, nv & 1, &sm.wc, a.status);
+#if MKKV_TC_PROF == 1
                     TC_STAMP(nv, 17);
+#endif
 #pragma unroll 1
                     for (int h = 0; h < 2; h++, oseq++) {
                         const int os = oseq % NOP;
                         tc_wait(&sm.op_full[os], (oseq / NOP) & 1, &sm.wc, a.status);
+#if MKKV_TC_PROF == 1
                         if (h == 0) TC_STAMP(nv, 18);
+#endif
                         tc_fence_after();
                         const unsigned a_lo = desc_lo(smem_u32(sm.op[os]), 128), dcol = tb + (h ? O_COL1 : O_COL0);
 #pragma unroll
@@ -578,7 +474,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                         umma_commit(&sm.op_empty[os]);
                     }
                     umma_commit(&sm.p_empty);
+#if MKKV_TC_PROF == 1
                     TC_STAMP(nv, 19);
+#endif
                     nv++;
                 }
             }
@@ -613,15 +511,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             // with the row so that the 16-byte loads of 8 consecutive lanes (rows 32 bits bytes apart) fall into 8 different
             // bank groups
             const int jr = (c + (lane >> (bits == 6 ? 1 : (bits == 5 || bits == 7) ? 2 : 0))) & 3;
-#pragma unroll 1
-            for (int h = 0; h < 2; h++) {
-                if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.wc, a.status);
-                dq_item_any(bits, smem_u32(sm.raw[rs]), lane, 4 * h + jr, valid, smem_u32(sm.op[os]) + 4 * jr * 2048 + pos_off);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.op_full[os]);
-                if (++os == NOP) os = 0, oph ^= 1, owrap = true;
-            }
+            // the packed bytes of both 128-dim halves are read first (they need no operand slot), then each half is written into its
+            // slot as that slot frees up
+            const unsigned rawa = smem_u32(sm.raw[rs]), off = 4 * jr * 2048 + pos_off;
+#define MKKV_SIDE(B)                                                                                                   \
+    {                                                                                                                  \
+        PackedBlock<B> b0, b1;                                                                                         \
+        dq_load<B>(b0, rawa, lane, jr, valid);                                                                         \
+        dq_load<B>(b1, rawa, lane, 4 + jr, valid);                                                                     \
+        if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.wc, a.status);                                               \
+        if (!(MKKV_ABL & 1)) dq_emit<B>(b0, smem_u32(sm.op[os]) + off);                                               \
+        fence_async_smem();                                                                                            \
+        __syncwarp();                                                                                                  \
+        if (lane == 0) mbar_arrive(&sm.op_full[os]);                                                                   \
+        if (++os == NOP) os = 0, oph ^= 1, owrap = true;                                                               \
+        if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.wc, a.status);                                               \
+        if (!(MKKV_ABL & 1)) dq_emit<B>(b1, smem_u32(sm.op[os]) + off);                                               \
+        fence_async_smem();                                                                                            \
+        __syncwarp();                                                                                                  \
+        if (lane == 0) mbar_arrive(&sm.op_full[os]);                                                                   \
+        if (++os == NOP) os = 0, oph ^= 1, owrap = true;                                                               \
+    }
+            const int fixed = side ? VB : KB; // the side's compiled-in main format, or 0: any
+            if (bits == 8) MKKV_SIDE(8)
+            else if (fixed == 4 || (!fixed && bits == 4)) MKKV_SIDE(4)
+            else if (fixed == 5 || (!fixed && bits == 5)) MKKV_SIDE(5)
+            else if (fixed == 6 || (!fixed && bits == 6)) MKKV_SIDE(6)
+            else if (fixed == 7 || !fixed) MKKV_SIDE(7)
+#undef MKKV_SIDE
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.raw_empty[rs]);
             if (st) TC_STAMP(grp, side ? 10 : 13);
@@ -682,6 +599,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
             const Task k = sm.tasks[j % NTASK];
             if (st) TC_STAMP(j, 1);
             tc_fence_after();
+#if !(MKKV_ABL & 4)
             unsigned rq[RS / 8][8];
 #pragma unroll
             for (int gq = 0; gq < RS / 8; gq++) scores_request(j, gq, rq[gq]);
@@ -699,6 +617,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     d[1] = make_float4(mx[4], mx[5], mx[6], mx[7]);
                 }
             }
+#endif
             named_bar(1 + c2, GT * 32);
             if (!batch && owner && q == 0 && k.nb > 1 && k.b + 1 < k.nb && exch_ok(k)) {
                 const float(&tm)[GT][AR] = sm.tmax[j % 3];
@@ -721,7 +640,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
         auto softmax = [&](int i, const Task & k) {
             if (st) TC_STAMP(i, 3);
             float beta = 0.f, f = 1.f;
-            if (owner) {
+            if (owner && !(MKKV_ABL & 8)) {
                 float m_in = batch && k.b > 0 ? carry : -CUDART_INF_F;
                 const size_t xb0 = xbase(k);
                 const bool alive = exch_ok(k);
@@ -794,6 +713,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm.s_empty[i % NSB]);
                 }
+#if MKKV_ABL & 2
+                for (int j = 0; j < 4; j++) hi[gq][j] = lo[gq][j] = __float_as_uint(s[j]);
+                continue;
+#endif
                 const float4 ma = *reinterpret_cast<const float4 *>(&W.m[8 * gq]), mb = *reinterpret_cast<const float4 *>(&W.m[8 * gq + 4]);
                 const float4 ba = *reinterpret_cast<const float4 *>(&W.beta[8 * gq]), bb = *reinterpret_cast<const float4 *>(&W.beta[8 * gq + 4]);
                 const uint4 bhv = *reinterpret_cast<const uint4 *>(&W.bh[4 * gq]), blv = *reinterpret_cast<const uint4 *>(&W.bl[4 * gq]);
@@ -929,6 +852,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_const
 
 static_assert(sizeof(tc::Smem) + 128 <= 232448, "shared memory of one CTA");
 size_t attend_tc_smem_bytes() { return sizeof(tc::Smem) + 128; }
+// the kernel instance for a job's main formats: the served presets are compiled in, anything else runs the any-format instance
+typedef void (*TcKernel)(const tc::Args);
+static TcKernel tc_kernel_for(int kb, int vb) {
+    if (kb == 5 && vb == 6) return tc::attn_tc_kernel<5, 6>;
+    if (kb == 5 && vb == 5) return tc::attn_tc_kernel<5, 5>;
+    if (kb == 6 && vb == 5) return tc::attn_tc_kernel<6, 5>;
+    if (kb == 8 && vb == 8) return tc::attn_tc_kernel<8, 8>;
+    return tc::attn_tc_kernel<0, 0>;
+}
+static const TcKernel tc_kernels[] = {tc::attn_tc_kernel<5, 6>, tc::attn_tc_kernel<5, 5>, tc::attn_tc_kernel<6, 5>, tc::attn_tc_kernel<8, 8>,
+                                      tc::attn_tc_kernel<0, 0>};
+// every instance may use the CTA's full shared memory (set once per device)
+static cudaError_t tc_prepare() {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        for (TcKernel k : tc_kernels) {
+            e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) attend_tc_smem_bytes());
+            if (e != cudaSuccess) return e;
+        }
+        attr_set[dev] = true;
+    }
+    return cudaSuccess;
+}
 // the wait limits of the launches that follow (process-wide; diagnostics and the failure-path test)
 static unsigned g_wait_hint_ns = tc::WAIT_HINT_NS, g_wait_rounds = tc::WAIT_ROUNDS, g_poll_rounds = tc::POLL_ROUNDS;
 void attend_tc_set_wait_limits(unsigned hint_ns, unsigned rounds, unsigned polls) {
@@ -939,7 +888,11 @@ void attend_tc_set_wait_limits(unsigned hint_ns, unsigned rounds, unsigned polls
 void attend_tc_default_wait_limits() { attend_tc_set_wait_limits(tc::WAIT_HINT_NS, tc::WAIT_ROUNDS, tc::POLL_ROUNDS); }
 cudaError_t preload_attend_tc() {
     cudaFuncAttributes fa;
-    return cudaFuncGetAttributes(&fa, (const void *) tc::attn_tc_kernel);
+    for (TcKernel k : tc_kernels) {
+        const cudaError_t e = cudaFuncGetAttributes(&fa, (const void *) k);
+        if (e != cudaSuccess) return e;
+    }
+    return tc_prepare();
 }
 
 cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, float2 * ml, int part_slots, unsigned long long * xa,
@@ -973,21 +926,14 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
     a.wait_hint_ns = g_wait_hint_ns;
     a.wait_rounds = g_wait_rounds;
     a.poll_rounds = g_poll_rounds;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    cudaError_t e = tc_prepare();
     if (e != cudaSuccess) return e;
-    if (dev < 64 && !attr_set[dev]) {
-        e = cudaFuncSetAttribute(tc::attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) attend_tc_smem_bytes());
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
     // the merge runs in the kernel's tail unless the caller wants the un-normalised partials (a later merge across GPUs)
     const bool fused = done && done_seq && !raw_part && job.O;
     a.done = fused ? done : nullptr;
     a.done_target = fused ? (*done_seq + 1u) * (unsigned) a.cph : 0u;
     void * args[] = {&a};
-    e = cudaLaunchCooperativeKernel((const void *) tc::attn_tc_kernel, dim3(NKV * a.cph), dim3(tc::NTHREADS), args, attend_tc_smem_bytes(), stream);
+    e = cudaLaunchCooperativeKernel((const void *) tc_kernel_for(job.kv.s[0].bits, job.kv.s[1].bits), dim3(NKV * a.cph), dim3(tc::NTHREADS), args, attend_tc_smem_bytes(), stream);
     if (e != cudaSuccess) return e;
     if (fused) {
         *done_seq += 1u;
@@ -1023,16 +969,13 @@ cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * job
     a.wait_hint_ns = g_wait_hint_ns;
     a.wait_rounds = g_wait_rounds;
     a.poll_rounds = g_poll_rounds;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    cudaError_t e = tc_prepare();
     if (e != cudaSuccess) return e;
-    if (dev < 64 && !attr_set[dev]) {
-        e = cudaFuncSetAttribute(tc::attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) attend_tc_smem_bytes());
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
-    tc::attn_tc_kernel<<<total_items, tc::NTHREADS, attend_tc_smem_bytes(), stream>>>(a);
+    // (the jobs of one batch may differ in format: the any-format instance unless they all share a compiled-in pair)
+    TcKernel kern = tc_kernel_for(jobs_host[0].kv.s[0].bits, jobs_host[0].kv.s[1].bits);
+    for (int j = 1; j < njobs; j++)
+        if (jobs_host[j].kv.s[0].bits != jobs_host[0].kv.s[0].bits || jobs_host[j].kv.s[1].bits != jobs_host[0].kv.s[1].bits) kern = tc::attn_tc_kernel<0, 0>;
+    kern<<<total_items, tc::NTHREADS, attend_tc_smem_bytes(), stream>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     return launch_merge(jobs_dev, jobs_host, njobs, max_T, part, ml, stream);
