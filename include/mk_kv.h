@@ -89,6 +89,14 @@ int mk_kv_attend_static(void * h, int seq, int layer, int n, int T, const void *
 int mk_kv_set_base(void * h, int seq, int base);
 int mk_kv_attend_partial(void * h, int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out);
 int mk_kv_combine(void * h, int layer, int T, int nparts, const void * parts, const void * mls, void * O);
+/* The two calls above for every layer of one decode step, so that the ranks exchange once per step instead of once per layer:
+ * mk_kv_step_layers_partial: layer l appends those of the T rows at n that fall into [own_lo, own_hi) (K, V + l kv_stride bytes, the
+ * step's T rows) and attends with Q + l q_stride over [pos_lo, min(pos_hi, n + T)); its partial goes to parts + l * 4 * 48 * 256
+ * floats and mls + l * 4 * 48 * 2 floats. mk_kv_combine_layers: parts [nparts][nlayers][4][48][256] and mls [nparts][nlayers][4][48][2]
+ * (the ranks' arrays gathered in rank order) -> O + l o_stride bytes, every layer in one launch. */
+int mk_kv_step_layers_partial(void * h, int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, size_t kv_stride,
+                              size_t q_stride, int own_lo, int own_hi, int pos_lo, int pos_hi, void * parts, void * mls);
+int mk_kv_combine_layers(void * h, int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride);
 /* append + attend of one decode step's layer, as the reference's attention phase does in one pass */
 int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O);
 /* One decode step over layers 0 .. nlayers - 1 in one call: layer l appends T rows at n from K + l kv_stride, V + l kv_stride

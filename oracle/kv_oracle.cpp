@@ -442,7 +442,7 @@ int orc_append(void * h, int layer, int pos0, int n, const uint16_t * K, const u
 // rotated). split > 1 cuts every chunk of the reference partition into that many pieces (partition-sensitivity probe).
 // Prologue qwen38_mk.cu:2876-2883, partition :2548-2573, merge :4658-4685.
 static int attend_impl(void * h, int layer, int n, int T, const uint16_t * Q, float * O, int nthreads, int split, float * out_m,
-                       float * out_l, float * out_O) {
+                       float * out_l, float * out_O, int ncuts = 0, const int * cuts = nullptr) {
     Cache & c = *static_cast<Cache *>(h);
     if (layer < 0 || layer >= c.layers || T < 1 || T > 8 || n < 0 || n + T > c.ctxp) { g_err = "orc_attend: out of range"; return -1; }
     const int L = n + T, R = GQ * T, ws = kv_ws(L, c.win);
@@ -452,7 +452,15 @@ static int attend_impl(void * h, int layer, int n, int T, const uint16_t * Q, fl
     std::vector<std::pair<int, int>> ch;
     for (int k = 0; k < nch; k++) {
         const int c0 = k * cs, c1 = std::min(L, c0 + cs);
-        if (split <= 1) ch.push_back({c0, c1});
+        if (ncuts > 0) { // the chunk cut again at the given positions (multiples of 32): a sequence split by position over GPUs
+            int a = c0;
+            for (int i = 0; i < ncuts; i++)
+                if (cuts[i] > a && cuts[i] < c1) {
+                    ch.push_back({a, cuts[i]});
+                    a = cuts[i];
+                }
+            ch.push_back({a, c1});
+        } else if (split <= 1) ch.push_back({c0, c1});
         else {
             const int tiles = (c1 - c0 + ATP - 1) / ATP, per = (tiles + split - 1) / split;
             for (int a = c0; a < c1; a += per * ATP) ch.push_back({a, std::min(c1, a + per * ATP)});
@@ -520,6 +528,11 @@ int orc_attend(void * h, int layer, int n, int T, const uint16_t * Q, float * O,
 // Op: [items][6 T][256]. O may be null (partials only). Returns the number of chunks per kv head, -1 on error.
 int orc_attend_parts(void * h, int layer, int n, int T, const uint16_t * Q, float * O, int nthreads, float * m, float * l, float * Op) {
     return attend_impl(h, layer, n, T, Q, O, nthreads, 1, m, l, Op);
+}
+// The same attention with the reference's chunks cut again at `cuts` (ascending positions, multiples of 32): what a sequence split by
+// position over several GPUs computes (every piece starts its running max afresh; the merge is the reference's).
+int orc_attend_cuts(void * h, int layer, int n, int T, const uint16_t * Q, float * O, int nthreads, int ncuts, const int * cuts) {
+    return attend_impl(h, layer, n, T, Q, O, nthreads, 1, nullptr, nullptr, nullptr, ncuts, cuts) < 0 ? -1 : 0;
 }
 // The merge alone (qwen38_mk.cu:4658-4685) over given partials of nc chunks per kv head in the layout above: O fp32 [T][24][256]
 void orc_merge_parts(int T, int nc, int rot_v, const float * pm, const float * pl, const float * pO, float * O) {

@@ -42,6 +42,7 @@ def lib():
         L.orc_has_ring.argtypes = [vp, ip, ip]
         L.orc_append.argtypes = [vp, ip, ip, ip, vp, vp]
         L.orc_attend.argtypes = [vp, ip, ip, ip, vp, vp, ip, ip]
+        L.orc_attend_cuts.argtypes = [vp, ip, ip, ip, vp, vp, ip, ip, vp]
         L.orc_attend_parts.argtypes = [vp, ip, ip, ip, vp, vp, ip, vp, vp, vp]
         L.orc_merge_parts.restype = None
         L.orc_merge_parts.argtypes = [ip, ip, ip, vp, vp, vp, vp]
@@ -184,6 +185,16 @@ class Cache:
         assert Q.shape == (T, NH, HD)
         O = np.zeros((T, NH, HD), dtype=np.float32)
         if lib().orc_attend(self.h, layer, n, T, _p(Q), _p(O), threads, split) != 0:
+            raise ValueError(err())
+        return O
+
+    def attend_cuts(self, layer, n, Q, cuts, threads=8):
+        """attend() with the reference's chunks cut again at the positions `cuts` (a sequence split by position over GPUs)"""
+        Q = np.ascontiguousarray(Q, dtype=np.float16)
+        T = Q.shape[0]
+        O = np.zeros((T, NH, HD), dtype=np.float32)
+        c = np.ascontiguousarray(sorted(int(x) for x in cuts), dtype=np.int32)
+        if lib().orc_attend_cuts(self.h, layer, n, T, _p(Q), _p(O), threads, len(c), _p(c)) != 0:
             raise ValueError(err())
         return O
 

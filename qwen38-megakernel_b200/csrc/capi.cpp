@@ -171,6 +171,19 @@ int mk_kv_combine(void * hp, int layer, int T, int nparts, const void * parts, c
         return 0;
     });
 }
+int mk_kv_step_layers_partial(void * hp, int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, size_t kv_stride,
+                              size_t q_stride, int own_lo, int own_hi, int pos_lo, int pos_hi, void * parts, void * mls) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->step_layers_partial(seq, nlayers, n, T, K, V, Q, kv_stride, q_stride, own_lo, own_hi, pos_lo, pos_hi, parts, mls);
+        return 0;
+    });
+}
+int mk_kv_combine_layers(void * hp, int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->combine_layers(nlayers, T, nparts, parts, mls, O, o_stride);
+        return 0;
+    });
+}
 int mk_kv_attend_static(void * hp, int seq, int layer, int n, int T, const void * Q, void * O) {
     return guarded(hp, [&](KvEngine * e) {
         e->attend_static(seq, layer, n, T, Q, O);

@@ -622,6 +622,53 @@ void KvEngine::combine(int layer, int T, int nparts, const void * parts, const v
     launches_ += 1;
 }
 
+// One decode step of a sequence split by position, all layers in one call (the host stays out of the per-layer loop): layer l
+// appends the rows of [n, n + T) that fall into [own_lo, own_hi) and attends over [pos_lo, min(pos_hi, n + T)); its partial goes to
+// parts + l * 4 * 48 * 256 floats and mls + l * 4 * 48 * 2 floats. The arrays of all ranks, gathered in rank order, are what
+// combine_layers takes.
+void KvEngine::step_layers_partial(int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, size_t kv_stride,
+                                   size_t q_stride, int own_lo, int own_hi, int pos_lo, int pos_hi, void * parts, void * mls) {
+    if (nlayers < 0 || nlayers > cfg_.layers) throw std::runtime_error("step_layers_partial: nlayers must be 0.." + std::to_string(cfg_.layers));
+    if (T < 1 || T > MAXT) throw std::runtime_error("step_layers_partial: T must be 1.." + std::to_string(MAXT));
+    const int a = std::max(n, own_lo), b = std::min(n + T, own_hi), hi = std::min(pos_hi, n + T);
+    for (int l = 0; l < nlayers; l++) {
+        if (b > a)
+            append(seq, l, a, b - a, static_cast<const char *>(K) + l * kv_stride + (size_t) (a - n) * NKV * HD * 2,
+                   static_cast<const char *>(V) + l * kv_stride + (size_t) (a - n) * NKV * HD * 2);
+        attend_partial(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, pos_lo, hi > pos_lo ? hi : pos_lo,
+                       static_cast<float *>(parts) + (size_t) l * NKV * AR * HD, static_cast<float *>(mls) + (size_t) l * NKV * AR * 2);
+    }
+}
+
+// The merge of every layer's partials in one launch: parts [nparts][nlayers][4][48][256], mls [nparts][nlayers][4][48][2] (the ranks'
+// step_layers_partial outputs gathered in rank order); layer l's output goes to O + l * o_stride bytes.
+void KvEngine::combine_layers(int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride) {
+    use_device();
+    if (nlayers < 1 || nlayers > cfg_.layers || T < 1 || T > MAXT || nparts < 1 || nparts > 64 || !parts || !mls || !O)
+        throw std::runtime_error("combine_layers: bad arguments");
+    ensure_work(work_items_, nlayers);
+    MKKV_CK(cudaEventSynchronize(ev_compute_)); // the previous upload of the job table has been consumed
+    for (int l = 0; l < nlayers; l++) {
+        AttnJob & j = h_jobs_[l];
+        j.kv = main_.views[l]; // (only the V rotation flag is read)
+        j.Q = nullptr;
+        j.O = reinterpret_cast<float *>(static_cast<char *>(O) + l * o_stride);
+        j.n = 0;
+        j.T = T;
+        j.nch = nparts;
+        j.cs = 0;
+        j.ws = 0;
+        j.item0 = l * NKV;          // partial p of kv head g of layer l is slot (p * nlayers + l) * 4 + g
+        j.pos_lo = j.pos_hi = 0;
+        j.pstride = nlayers * NKV;
+    }
+    MKKV_CK(cudaMemcpyAsync(d_jobs_, h_jobs_, sizeof(AttnJob) * nlayers, cudaMemcpyHostToDevice, stream_));
+    MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    MKKV_CK(launch_merge(d_jobs_, h_jobs_, nlayers, T, const_cast<float *>(static_cast<const float *>(parts)),
+                         const_cast<float2 *>(static_cast<const float2 *>(mls)), stream_));
+    launches_ += 1;
+}
+
 void KvEngine::attend_static(int seq, int layer, int n, int T, const void * Q, void * O) {
     use_device();
     check_layer(layer);

@@ -52,6 +52,8 @@ def load_library():
         "mk_kv_set_base": (i, [vp, i, i]),
         "mk_kv_attend_partial": (i, [vp, i, i, i, i, vp, i, i, vp, vp]),
         "mk_kv_combine": (i, [vp, i, i, i, vp, vp, vp]),
+        "mk_kv_step_layers_partial": (i, [vp, i, i, i, i, vp, vp, vp, C.c_size_t, C.c_size_t, i, i, i, i, vp, vp]),
+        "mk_kv_combine_layers": (i, [vp, i, i, i, vp, vp, vp, C.c_size_t]),
         "mk_kv_step": (i, [vp, i, i, i, i, vp, vp, vp, vp]),
         "mk_kv_step_layers": (i, [vp, i, i, i, i, vp, vp, vp, vp, C.c_size_t, C.c_size_t, C.c_size_t]),
         "mk_kv_reserve_batch": (i, [vp, i]),
@@ -215,6 +217,18 @@ class Engine:
     def combine(self, layer, T, nparts, parts, mls, O):
         """merge of nparts partial results (all-gathered) into O [T][24][256]"""
         self._ck(self.L.mk_kv_combine(self.h, layer, T, nparts, _ptr(parts), _ptr(mls), _ptr(O)), "combine")
+
+    def step_layers_partial(self, n, K, V, Q, own_lo, own_hi, pos_lo, pos_hi, parts, mls, seq=SEQ_MAIN):
+        """K, V [layers][T][4][256], Q [layers][T][24][256] (layer stride = the tensors' stride 0); parts [layers][4][48][256],
+        mls [layers][4][48][2]"""
+        self._ck(self.L.mk_kv_step_layers_partial(self.h, seq, Q.shape[0], n, Q.shape[1], _ptr(K[0]), _ptr(V[0]), _ptr(Q[0]),
+                                                  K.stride(0) * K.element_size(), Q.stride(0) * Q.element_size(), own_lo, own_hi, pos_lo, pos_hi,
+                                                  _ptr(parts), _ptr(mls)), "step_layers_partial")
+
+    def combine_layers(self, T, nparts, parts, mls, O):
+        """parts [nparts][layers][4][48][256], mls [nparts][layers][4][48][2] -> O [layers][T][24][256]"""
+        self._ck(self.L.mk_kv_combine_layers(self.h, O.shape[0], T, nparts, _ptr(parts), _ptr(mls), _ptr(O[0]), O.stride(0) * O.element_size()),
+                 "combine_layers")
 
     def step(self, layer, n, K, V, Q, O, seq=SEQ_MAIN):
         self._ck(self.L.mk_kv_step(self.h, seq, layer, n, Q.shape[0], _ptr(K), _ptr(V), _ptr(Q), _ptr(O)), "step")
