@@ -6,8 +6,11 @@
 //
 // Parity pin: the quantizer, rotation and dequantisation are checked against the reference's own device functions
 // (cut from its source at build time into oracle/_ref and run on a GPU; see oracle/ref_witness.cu) through the golden
-// vectors in tests/golden/. The attention arithmetic has no stored vectors in the reference; it follows the cited
-// lines and is pinned only through the quantized operands it consumes.
+// vectors in tests/golden/kv_quant_golden.npz. The attention arithmetic is checked against the reference's own decode-attention
+// kernels (cut from its source by its own generator script and run on a GPU behind oracle/ref_attn_witness.cu): the per-chunk
+// running maxima, sums and un-normalised outputs and the merged output those kernels produced on seeded caches are stored in
+// tests/golden/attn_golden.npz (made by tests/golden/make_attn_golden.py), together with the rows the reference's store
+// kernels wrote, which must equal this file's bytes.
 //
 // Every function cites the reference lines it follows (paths relative to the reference project root).
 #include <algorithm>

@@ -39,7 +39,7 @@ template <int BITS> MKKV_HD unsigned pair_sub_b() { return MAGIC_B + (0x00100010
 template <int BITS> MKKV_HD bool pair_is_a(int p) { return BITS >= 7 || !(p & 1); }
 
 // Lane word `word` of a 4 .. 6-bit row and its high bits -> the four pairs. hi: BITS == 5: the word's byte of high bits (bit k:
-// value k); BITS == 6: its 16 bits (bits 2 k, 2 k + 1: value k); other bits of hi must be zero.
+// value k), no other bit set; BITS == 6: its 16 bits (bits 2 k, 2 k + 1: value k), higher bits are ignored.
 template <int BITS> MKKV_HD void pair_words(unsigned word, unsigned hi, unsigned (&x)[4]) {
     static_assert(BITS >= 4 && BITS <= 6, "pair_words: 4 .. 6 bits");
     const unsigned w8 = word >> 8;

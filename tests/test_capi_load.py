@@ -20,7 +20,7 @@ def test_header_declares_the_reference_names():
     for n in ("mk_last_error", "mk_free", "mk_reset", "mk_truncate", "mk_rewind_to", "mk_checkpoints", "mk_state_digest",
               "mk_store_budget", "mk_store_reserve", "mk_store_info", "mk_kv_sizes", "mk_park", "mk_unpark", "mk_park_drop",
               "mk_park_need", "mk_park_bytes", "mk_side_begin", "mk_side_end", "mk_side_drop", "mk_side_active", "mk_slots_open",
-              "mk_build_info"):
+              "mk_slots_open2", "mk_side_end_park", "mk_side_unpark", "mk_rewind_to_checkpoint", "mk_build_info"):
         assert n in names
 
 
