@@ -53,7 +53,7 @@ def algorithmic_bytes(n, T, kbits=5, vbits=6, win=WIN):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs"""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the warm-up and timed steps run"""
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
@@ -65,7 +65,7 @@ class ClockSampler:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=f, stderr=subprocess.DEVNULL)
+                                          "-lms", "50"], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -602,10 +602,10 @@ def main():
             ms = float(t.item())
         return ms, eng.launches() - l0, state["bytes"]
 
-    for _ in range(args.warmup):
-        one_step()
     sampler = ClockSampler(local_rank)
     sampler.start()
+    for _ in range(args.warmup):
+        one_step()
     # --- device-resident timing: REPEATS runs of the K-step loop; the line reports the median run ---
     runs = [timed_steps(False) for _ in range(REPEATS)]
     order = sorted(range(REPEATS), key=lambda i: runs[i][0])

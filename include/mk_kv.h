@@ -140,6 +140,19 @@ int mk_store_reserve(void * h, long long bytes);
  * microseconds */
 int mk_store_info(void * h, long long * out, int cap);
 void mk_kv_sizes(void * h, long long * per_token, long long * rings, long long * state, long long * checkpoint);
+/* The reference's prompt-state file for the KV regions (state_files.cu:97-238; the reference reaches it through MK_STATE inside its
+ * generate call, engine.cu:1078-1130, and has no export for it): "MKSTATE1", u64 key length, key, u64 hend, u64 region count, u64
+ * size of each region, then the regions: for every layer, side, kv head the values of rows 0 .. hend - 1 and their scales; for every
+ * (layer, side) with a ring all heads' ring values, then all heads' ring scales; then n_extra caller regions (the reference appends
+ * its recurrent-state buffers dstate, conv, h_hist there; device or host pointers). key is the caller's identity string of the state
+ * (state_files.cu:44-95 builds it from the model file, the KV layout, the environment and the token prefix).
+ * mk_kv_state_save: hend must equal the rows written; written to path + ".tmp<pid>" and renamed. Returns the file's size, -1 on error.
+ * mk_kv_state_load: 1 = restored (the sequence then holds hend committed positions), 0 = no file or it does not match key, hend
+ * or a region size (the caller recomputes and saves again), -1 error. */
+long long mk_kv_state_save(void * h, int seq, const char * path, const void * key, size_t key_len, int hend, const void * const * extra,
+                           const size_t * extra_sizes, int n_extra);
+int mk_kv_state_load(void * h, int seq, const char * path, const void * key, size_t key_len, int hend, void * const * extra,
+                     const size_t * extra_sizes, int n_extra);
 /* id > 0, 0 (empty sequence), -3 (no room in the store), -1 error */
 int mk_park(void * h, int max_checkpoints);
 int mk_kv_park(void * h, int seq, int max_checkpoints);

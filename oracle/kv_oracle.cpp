@@ -685,4 +685,47 @@ long long orc_snapshot(void * h, int a, int b, int ra, int rb, uint8_t * out) {
     return pos;
 }
 
+// The prompt-state file of the KV regions, state_files.cu:97-238: "MKSTATE1", u64 key length, key bytes, u64 hend, u64 region
+// count, u64 size of every region, then the regions' bytes: for every layer, side, kv head the values of rows 0 .. hend - 1 and
+// their scales (:103-110); then for every (layer, side) with a ring ALL heads' ring values, then all heads' ring scales
+// (:115-119); then the caller's extra regions (the reference's own are its recurrent state: dstate, conv, h_hist, :120-122).
+// Written to path + ".tmp<pid>" and renamed (:136, 178). Returns the file's size, -1 on an I/O error.
+long long orc_state_save(void * h, const char * path, const uint8_t * key, long long key_len, int hend, int n_extra, const uint8_t * const * extra,
+                         const long long * extra_sizes) {
+    Cache & c = *static_cast<Cache *>(h);
+    if (hend < 0 || hend > c.ctx) return -1;
+    std::vector<std::pair<const void *, size_t>> R;
+    for (int l = 0; l < c.layers; l++)
+        for (int w = 0; w < 2; w++)
+            for (int g = 0; g < NKV; g++) {
+                R.push_back({c.vrow(w, l, g, 0), (size_t) hend * row_bytes(c.kvb[w][l])});
+                R.push_back({c.srow(w, l, g, 0), (size_t) hend * 16});
+            }
+    for (int l = 0; l < c.layers; l++)
+        for (int w = 0; w < 2; w++)
+            if (c.has_ring[w][l]) {
+                R.push_back({c.rval[w][l].data(), (size_t) NKV * c.rc * HD});
+                R.push_back({c.rsc[w][l].data(), (size_t) NKV * c.rc * 16});
+            }
+    for (int i = 0; i < n_extra; i++) R.push_back({extra[i], (size_t) extra_sizes[i]});
+    const std::string tmp = std::string(path) + ".tmp.oracle";
+    FILE * f = fopen(tmp.c_str(), "wb");
+    if (!f) return -1;
+    bool ok = fwrite("MKSTATE1", 8, 1, f) == 1;
+    auto w64 = [&](uint64_t v) { ok = ok && fwrite(&v, 8, 1, f) == 1; };
+    w64((uint64_t) key_len);
+    ok = ok && (key_len == 0 || fwrite(key, 1, (size_t) key_len, f) == (size_t) key_len);
+    w64((uint64_t) hend);
+    w64(R.size());
+    long long tot = 8 + 8 + key_len + 8 + 8 + 8 * (long long) R.size();
+    for (const auto & r : R) w64(r.second), tot += (long long) r.second;
+    for (const auto & r : R) ok = ok && (r.second == 0 || fwrite(r.first, 1, r.second, f) == r.second);
+    ok = (fclose(f) == 0) && ok;
+    if (!ok || rename(tmp.c_str(), path) != 0) {
+        remove(tmp.c_str());
+        return -1;
+    }
+    return tot;
+}
+
 } // extern "C"

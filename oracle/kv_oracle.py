@@ -56,6 +56,8 @@ def lib():
         L.orc_digest.argtypes = [vp, ip, vp, C.c_longlong]
         L.orc_snapshot.restype = C.c_longlong
         L.orc_snapshot.argtypes = [vp, ip, ip, ip, ip, vp]
+        L.orc_state_save.restype = C.c_longlong
+        L.orc_state_save.argtypes = [vp, cp, vp, C.c_longlong, ip, ip, vp, vp]
         L.orc_quant_row.argtypes = [vp, ip, vp, vp]
         L.orc_dequant_f32.argtypes = [vp, vp, ip, vp]
         L.orc_dequant_f16.argtypes = [vp, vp, ip, vp]
@@ -251,6 +253,17 @@ class Cache:
         out = np.zeros(cnt, dtype=np.uint64)
         lib().orc_digest(self.h, n, _p(out), cnt)
         return out
+
+    def state_save(self, path, key, hend, extra=()):
+        """the reference's prompt-state file of rows 0 .. hend - 1 + the rings + the caller's extra regions (bytes objects)"""
+        bufs = [np.frombuffer(bytes(e), dtype=np.uint8) for e in extra]
+        ptrs = (C.c_void_p * max(len(bufs), 1))(*[b.ctypes.data if b.size else None for b in bufs])
+        sizes = (C.c_longlong * max(len(bufs), 1))(*[b.size for b in bufs])
+        kb = np.frombuffer(bytes(key), dtype=np.uint8)
+        n = lib().orc_state_save(self.h, str(path).encode(), kb.ctypes.data if kb.size else None, kb.size, hend, len(bufs), ptrs, sizes)
+        if n < 0:
+            raise ValueError("state_save failed")
+        return n
 
     def snapshot(self, a, b, ra=0, rb=None):
         rb = self.rc if rb is None else rb

@@ -302,6 +302,19 @@ int mk_kv_park(void * hp, int seq, int max_checkpoints) {
         return id < 0 ? -3 : id;
     });
 }
+long long mk_kv_state_save(void * hp, int seq, const char * path, const void * key, size_t key_len, int hend, const void * const * extra,
+                           const size_t * extra_sizes, int n_extra) {
+    long long r = -1;
+    guarded(hp, [&](KvEngine * e) {
+        r = e->state_save(seq, path, key, key_len, hend, extra, extra_sizes, n_extra);
+        return 0;
+    });
+    return r;
+}
+int mk_kv_state_load(void * hp, int seq, const char * path, const void * key, size_t key_len, int hend, void * const * extra,
+                     const size_t * extra_sizes, int n_extra) {
+    return guarded(hp, [&](KvEngine * e) { return e->state_load(seq, path, key, key_len, hend, extra, extra_sizes, n_extra) ? 1 : 0; });
+}
 int mk_park(void * hp, int max_checkpoints) { return mk_kv_park(hp, MK_SEQ_MAIN, max_checkpoints); }
 int mk_kv_unpark(void * hp, int seq, int id) {
     return guarded(hp, [&](KvEngine * e) {

@@ -68,7 +68,7 @@ static_assert(12 * 80 + 16 * 56 + 4 * 40 <= 32 * 64, "register shares");
 static_assert(8 * 112 + 16 * 56 + 4 * 56 <= 28 * 72, "register shares");
 #endif
 constexpr int RAW_SLOT = ATP * HD + ATP * SCALE_ROW; // one tile of the widest format and its scales: 8704 bytes
-constexpr int NRAW = 9;
+constexpr int NRAW = 8;
 constexpr int OP_SLOT = GP * 128 * 2;       // fp16 operand: 128 positions x 128 dims
 constexpr int NOP = 3;
 constexpr int NSB = 5;                      // S^T buffers: K runs NSB groups ahead of V
@@ -98,8 +98,8 @@ struct Smem {
     uint8_t raw[NRAW][RAW_SLOT];
     uint8_t q[Q_BYTES];         // [dim group 32][row group 6][8 rows][8 dims]
     uint8_t p[2][P_BYTES];      // high / low part: [row group 6][position group 16][8 positions][8 rows]
-    float tmax[3][GT][AR];      // row maxima of a group's tiles; by group % 3: a group's maxima are read while the next group's
-                                // are written, and a warp is never two groups ahead of its slice.
+    float tmax[4][GT][AR];      // row maxima of a group's tiles; by group % 4: a group's maxima are read while those of the next two
+                                // groups exist or are being written, and a warp is never a whole group ahead of its slice.
                                 // The first buffer holds the row sums at the end.
     WarpScratch ws[NSOFT];
     unsigned char rtok[AR];     // token of a query row
@@ -612,7 +612,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
 #pragma unroll
                 for (int i = 0; i < 8; i++) mx[i] = warp_max(s[i]);
                 if (lane == 0) {
-                    float4 * d = reinterpret_cast<float4 *>(&sm.tmax[j % 3][q][row0 + 8 * gq]);
+                    float4 * d = reinterpret_cast<float4 *>(&sm.tmax[j & 3][q][row0 + 8 * gq]);
                     d[0] = make_float4(mx[0], mx[1], mx[2], mx[3]);
                     d[1] = make_float4(mx[4], mx[5], mx[6], mx[7]);
                 }
@@ -620,7 +620,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
 #endif
             named_bar(1 + c2, GT * 32);
             if (!batch && owner && q == 0 && k.nb > 1 && k.b + 1 < k.nb && exch_ok(k)) {
-                const float(&tm)[GT][AR] = sm.tmax[j % 3];
+                const float(&tm)[GT][AR] = sm.tmax[j & 3];
                 const float gk = fmaxf(fmaxf(tm[0][r_own], tm[1][r_own]), fmaxf(tm[2][r_own], tm[3][r_own]));
                 __stcg(a.xa + xbase(k) + (size_t) k.b * AR, ((unsigned long long) (unsigned) a.epoch << 32) | __float_as_uint(gk));
             }
@@ -650,7 +650,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
                     if (k.b >= 3) m_in = fmaxf(m_in, poll_word(a.xb + xb0 + (size_t) (k.b - 3) * AR, w0, a.epoch, &sm.wc, a.status));
                 }
                 if (st) TC_STAMP(i, 7);
-                const float(&tm)[GT][AR] = sm.tmax[i % 3];
+                const float(&tm)[GT][AR] = sm.tmax[i & 3];
                 float mr = m_in; // running max after this warp's tile, M: after the whole group
 #pragma unroll
                 for (int t = 0; t < GT; t++)
@@ -771,13 +771,17 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         };
 
         if (G > 0) {
-            for (int i = -1; i < G; i++) { // maxima of group i + 1, then P of group i (tasks: left by the producer, see there)
-                if (i + 1 < G) maxima(i + 1);
+            // maxima of group i + MAX_AHEAD, then P of group i (tasks: left by the producer, see there). The maxima run two groups
+            // ahead of P so that a group's own maxima are published well before the CTAs that hold the chunk's next groups need
+            // them: the CTAs of a kv head may drift apart by a group without a poll having to wait
+            constexpr int MAX_AHEAD = 2;
+            for (int i = -MAX_AHEAD; i < G; i++) {
+                if (i + MAX_AHEAD < G) maxima(i + MAX_AHEAD);
                 if (i >= 0) {
                     const Task kc = sm.tasks[i % NTASK];
                     softmax(i, kc);
                 }
-                if (i + 1 < G) {
+                if (i + 1 >= 0 && i + 1 < G) {
                     const Task kn = sm.tasks[(i + 1) % NTASK];
                     request_words(kn);
                 }

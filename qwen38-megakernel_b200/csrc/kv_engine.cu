@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <unistd.h>
 
 namespace mkkv {
 
@@ -959,6 +960,151 @@ size_t KvEngine::park_bytes(int id) const {
     const auto it = parked_.find(id);
     return it == parked_.end() ? 0 : it->second.blob.used;
 }
+// ---- prompt-state file (state_files.cu:97-238) ----
+// The regions in the file's order: for every layer, side, kv head the values of rows 0 .. hend - 1, then their scales (:103-110);
+// then for every (layer, side) with a ring all heads' ring values, then all heads' ring scales (:115-119).
+std::vector<std::pair<char *, size_t>> KvEngine::state_regions(Seq & s, int hend) const {
+    std::vector<std::pair<char *, size_t>> r;
+    for (int l = 0; l < cfg_.layers; l++)
+        for (int w = 0; w < 2; w++) {
+            const KvSide & sd = s.views[l].s[w];
+            for (int g = 0; g < NKV; g++) {
+                r.push_back({reinterpret_cast<char *>(sd.val + (size_t) g * s.ctxp * row_bytes(sd.bits)), (size_t) hend * row_bytes(sd.bits)});
+                r.push_back({reinterpret_cast<char *>(sd.sc + (size_t) g * s.ctxp * 8), (size_t) hend * SCALE_ROW});
+            }
+        }
+    for (int l = 0; l < cfg_.layers; l++)
+        for (int w = 0; w < 2; w++) {
+            const KvSide & sd = s.views[l].s[w];
+            if (!sd.rval) continue;
+            r.push_back({reinterpret_cast<char *>(sd.rval), (size_t) NKV * rc_ * HD});
+            r.push_back({reinterpret_cast<char *>(sd.rsc), (size_t) NKV * rc_ * SCALE_ROW});
+        }
+    return r;
+}
+
+namespace {
+constexpr char STATE_MAGIC[9] = "MKSTATE1";
+constexpr size_t STATE_PIECE = (size_t) 32 << 20;
+struct PinnedPiece { // one pinned staging buffer for the file's pieces
+    uint8_t * p = nullptr;
+    PinnedPiece() { if (cudaHostAlloc(reinterpret_cast<void **>(&p), STATE_PIECE, cudaHostAllocDefault) != cudaSuccess) p = nullptr, cudaGetLastError(); }
+    ~PinnedPiece() { if (p) cudaFreeHost(p); }
+};
+} // namespace
+
+long long KvEngine::state_save(int seq, const char * path, const void * key, size_t key_len, int hend, const void * const * extra,
+                               const size_t * extra_sizes, int n_extra) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    need_whole(s, "state_save");
+    if (!path || (key_len && !key) || n_extra < 0 || (n_extra && (!extra || !extra_sizes))) throw std::runtime_error("state_save: null argument");
+    if (hend < 0 || hend != s.kv_top)
+        throw std::runtime_error("state_save: hend (" + std::to_string(hend) + ") must equal the rows written (" + std::to_string(s.kv_top) + "): the rings in the file are those of exactly that state");
+    for (int l = 0; l < cfg_.layers; l++) spill_to(s, l, hend); // spill mode: every position gets its main-format row first
+    wait_copies(s);
+    MKKV_CK(cudaStreamSynchronize(stream_));
+    auto R = state_regions(s, hend);
+    for (int i = 0; i < n_extra; i++) R.push_back({static_cast<char *>(const_cast<void *>(extra[i])), extra_sizes[i]});
+    const std::string tmp = std::string(path) + ".tmp" + std::to_string((long long) getpid());
+    FILE * f = fopen(tmp.c_str(), "wb");
+    if (!f) throw std::runtime_error(std::string("state_save: cannot write ") + tmp);
+    bool ok = fwrite(STATE_MAGIC, 8, 1, f) == 1;
+    auto w64 = [&](uint64_t v) { ok = ok && fwrite(&v, 8, 1, f) == 1; };
+    w64(key_len);
+    ok = ok && (key_len == 0 || fwrite(key, 1, key_len, f) == key_len);
+    w64((uint64_t) hend);
+    w64(R.size());
+    long long tot = 8 + 8 + (long long) key_len + 8 + 8 + 8 * (long long) R.size();
+    for (const auto & r : R) w64(r.second), tot += (long long) r.second;
+    PinnedPiece buf;
+    if (!buf.p) {
+        fclose(f);
+        unlink(tmp.c_str());
+        throw std::runtime_error("state_save: no pinned staging buffer");
+    }
+    try {
+        for (const auto & r : R)
+            for (size_t o = 0; ok && o < r.second; o += STATE_PIECE) {
+                const size_t n = std::min(STATE_PIECE, r.second - o);
+                MKKV_CK(cudaMemcpy(buf.p, r.first + o, n, cudaMemcpyDefault));
+                ok = fwrite(buf.p, 1, n, f) == n;
+            }
+    } catch (...) { // (a CUDA error: no half-written file is left behind, state_files.cu:163-167)
+        fclose(f);
+        unlink(tmp.c_str());
+        throw;
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok || rename(tmp.c_str(), path) != 0) {
+        unlink(tmp.c_str());
+        throw std::runtime_error(std::string("state_save: writing ") + path + " failed");
+    }
+    return tot;
+}
+
+bool KvEngine::state_load(int seq, const char * path, const void * key, size_t key_len, int hend, void * const * extra, const size_t * extra_sizes,
+                          int n_extra) {
+    use_device();
+    Seq & s = seq_ref(seq);
+    need_whole(s, "state_load");
+    if (!path || (key_len && !key) || n_extra < 0 || (n_extra && (!extra || !extra_sizes))) throw std::runtime_error("state_load: null argument");
+    if (hend < 0 || hend > s.ctx) throw std::runtime_error("state_load: hend " + std::to_string(hend) + " does not fit the sequence's context");
+    if (seq == SEQ_MAIN && sw_on_) throw std::runtime_error("state_load: a side request is active");
+    FILE * f = fopen(path, "rb");
+    if (!f) return false;
+    auto R = state_regions(s, hend);
+    for (int i = 0; i < n_extra; i++) R.push_back({static_cast<char *>(extra[i]), extra_sizes[i]});
+    // the header must name this very state: key, hend, region count and every region's size, and the file must end with the
+    // last region (state_files.cu:206-216); anything else is "no state file" and the caller rebuilds it
+    bool ok = true;
+    auto r64 = [&](uint64_t & v) { return fread(&v, 8, 1, f) == 1; };
+    char magic[8];
+    ok = fread(magic, 8, 1, f) == 1 && !memcmp(magic, STATE_MAGIC, 8);
+    uint64_t kn = 0, h = 0, nr = 0, v = 0;
+    ok = ok && r64(kn) && kn == key_len;
+    if (ok && kn) {
+        std::vector<char> kb(kn);
+        ok = fread(kb.data(), 1, kn, f) == kn && !memcmp(kb.data(), key, kn);
+    }
+    ok = ok && r64(h) && h == (uint64_t) hend && r64(nr) && nr == R.size();
+    unsigned long long tot = 0;
+    for (size_t i = 0; ok && i < R.size(); i++) ok = r64(v) && v == R[i].second, tot += R[i].second;
+    if (ok) {
+        const long at = ftell(f);
+        ok = at >= 0 && fseek(f, 0, SEEK_END) == 0 && (unsigned long long) ftell(f) == (unsigned long long) at + tot && fseek(f, at, SEEK_SET) == 0;
+    }
+    if (!ok) {
+        fclose(f);
+        return false;
+    }
+    PinnedPiece buf;
+    if (!buf.p) {
+        fclose(f);
+        throw std::runtime_error("state_load: no pinned staging buffer");
+    }
+    reset(seq);
+    wait_copies(s);
+    MKKV_CK(cudaStreamSynchronize(stream_)); // (no earlier launch still reads the state, state_files.cu:217)
+    try {
+        for (const auto & r : R)
+            for (size_t o = 0; o < r.second; o += STATE_PIECE) {
+                const size_t n = std::min(STATE_PIECE, r.second - o);
+                if (fread(buf.p, 1, n, f) != n) throw std::runtime_error(std::string("state_load: short read of ") + path);
+                MKKV_CK(cudaMemcpy(r.first + o, buf.p, n, cudaMemcpyDefault));
+            }
+    } catch (...) {
+        fclose(f);
+        reset(seq); // (rows partly overwritten: the sequence is empty)
+        throw;
+    }
+    fclose(f);
+    s.n = hend;
+    s.kv_top = hend; // (as a prefill of 0 .. hend - 1, state_files.cu:241)
+    std::fill(s.spilled.begin(), s.spilled.end(), hend);
+    return true;
+}
+
 int KvEngine::park_len(int id) const {
     const auto it = parked_.find(id);
     return it == parked_.end() ? -1 : it->second.n;

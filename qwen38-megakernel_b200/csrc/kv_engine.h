@@ -117,6 +117,12 @@ class KvEngine {
     };
     StoreInfo store_info() const;
     void kv_sizes(size_t * per_token, size_t * rings, size_t * state, size_t * checkpoint) const;
+    // The reference's prompt-state file (state_files.cu:97-238) of rows 0 .. hend - 1, the rings and the caller's extra regions
+    // (device or host pointers). save: the file's size; load: true when the file exists and matches key, hend and every region size.
+    long long state_save(int seq, const char * path, const void * key, size_t key_len, int hend, const void * const * extra,
+                         const size_t * extra_sizes, int n_extra);
+    bool state_load(int seq, const char * path, const void * key, size_t key_len, int hend, void * const * extra, const size_t * extra_sizes,
+                    int n_extra);
     int park(int seq, int max_checkpoints, bool wait = true); // id > 0; 0: empty sequence; -1: no room
     bool unpark(int seq, int id, bool wait = true);
     bool restore_prefix(int seq, int id, int P, bool wait = true); // rows [0, P) of a parked entry; rings refilled; entry kept
@@ -180,6 +186,7 @@ class KvEngine {
     void need_whole(const Seq & s, const char * what) const;
     AttnJob whole_job(const Seq & s, const char * what, int layer, int n, int T, const void * Q, void * O) const;
     void unpark_into(Seq & s, int seq, int id);
+    std::vector<std::pair<char *, size_t>> state_regions(Seq & s, int hend) const;
     void spill_to(Seq & s, int layer, int upto);
     void ring_rewind(Seq & s, int P);
     void drop_checkpoints(Seq & s, int after);

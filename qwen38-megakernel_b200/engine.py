@@ -79,6 +79,8 @@ def load_library():
         "mk_unpark": (i, [vp, i]),
         "mk_kv_unpark": (i, [vp, i, i]),
         "mk_park_drop": (i, [vp, i]),
+        "mk_kv_state_save": (ll, [vp, i, cp, cp, C.c_size_t, i, vp, vp, i]),
+        "mk_kv_state_load": (i, [vp, i, cp, cp, C.c_size_t, i, vp, vp, i]),
         "mk_park_need": (ll, [vp, i]),
         "mk_park_bytes": (ll, [vp, i]),
         "mk_kv_restore_prefix": (i, [vp, i, i, i, i]),
@@ -310,6 +312,24 @@ class Engine:
 
     def park_drop(self, pid):
         return self.L.mk_park_drop(self.h, pid) == 0
+
+    def state_save(self, path, key, hend, extra=(), seq=SEQ_MAIN):
+        """The reference's prompt-state file (state_files.cu:97-238) of rows 0 .. hend - 1 + the rings + the caller's extra regions
+        (torch tensors, device or host). Returns the file's size."""
+        import ctypes as C
+        key = bytes(key)
+        ptrs = (C.c_void_p * max(len(extra), 1))(*[t.data_ptr() for t in extra])
+        sizes = (C.c_size_t * max(len(extra), 1))(*[t.numel() * t.element_size() for t in extra])
+        r = self.L.mk_kv_state_save(self.h, seq, str(path).encode(), key, len(key), hend, ptrs, sizes, len(extra))
+        return self._ck(r, "state_save")
+
+    def state_load(self, path, key, hend, extra=(), seq=SEQ_MAIN):
+        """True when the file exists and matches key, hend and every region size: the sequence then holds hend positions."""
+        import ctypes as C
+        key = bytes(key)
+        ptrs = (C.c_void_p * max(len(extra), 1))(*[t.data_ptr() for t in extra])
+        sizes = (C.c_size_t * max(len(extra), 1))(*[t.numel() * t.element_size() for t in extra])
+        return self._ck(self.L.mk_kv_state_load(self.h, seq, str(path).encode(), key, len(key), hend, ptrs, sizes, len(extra)), "state_load") == 1
 
     def park_need(self, max_cks=0):
         return self.L.mk_park_need(self.h, max_cks)
