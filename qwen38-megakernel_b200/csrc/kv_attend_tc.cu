@@ -44,28 +44,30 @@ namespace tc {
 
 using namespace attn_common;
 
-#ifndef MKKV_TC_NSL
-#define MKKV_TC_NSL 2 // row slices of the softmax warps: 3 (12 warps x 16 rows, 1024 threads) or 2 (8 warps x 24 rows, 896 threads)
+#ifndef MKKV_TC_NDQ
+#define MKKV_TC_NDQ 16 // unpack warps: 16 (one 32-dim block of a half each, 28 warps per CTA) or 8 (two blocks each, 20 warps: measured
+                       // 115 us against 105 on the one-layer case, the unpack needs the warps)
 #endif
-constexpr int NSL = MKKV_TC_NSL;
+constexpr int NSL = 2;         // row slices of the softmax warps: 24 query rows each
 constexpr int NSOFT = 4 * NSL; // softmax warps first: warp = 4 c2 + q, tile q (tensor-memory lanes 32 q ..), query rows RS c2 .. + RS - 1
-constexpr int NDQ = 16;        // then the unpack warps: 4 c + q, tile q, dims 32 (4 h + c) .. + 31 of half h
+constexpr int NDQ = MKKV_TC_NDQ; // then the unpack warps: 4 c + q, tile q, 32-dim blocks c, c + NDQ / 4, .. of each 128-dim half
+constexpr int BPW = 16 / NDQ;  // blocks of a half per unpack warp
 constexpr int W_ISSUE = NSOFT + NDQ, W_PROD = W_ISSUE + 1;
 constexpr int NTHREADS = (W_PROD + 3) * 32; // two idle warps complete the last group of four (register reallocation is per group)
 constexpr int GT = 4, GP = GT * ATP;        // tiles / positions per group: the M of one MMA
 constexpr int RS = AR / NSL;                // query rows per softmax warp
 // registers per thread after the reallocation (the launch gives 65536 / NTHREADS rounded down to 8; the three shares sum to at
 // most the CTA's launch allocation -- a larger sum faults)
-#if MKKV_TC_NSL == 3
-#define MKKV_TC_REGS_SOFT "80"
-#define MKKV_TC_REGS_DQ "56"
-#define MKKV_TC_REGS_CTL "40"
-static_assert(12 * 80 + 16 * 56 + 4 * 40 <= 32 * 64, "register shares");
+#if MKKV_TC_NDQ == 8
+#define MKKV_TC_REGS_SOFT "128"
+#define MKKV_TC_REGS_DQ "80"
+#define MKKV_TC_REGS_CTL "56"
+static_assert(NTHREADS == 640 && 8 * 128 + 8 * 80 + 4 * 56 <= 20 * 96, "register shares");
 #else
 #define MKKV_TC_REGS_SOFT "112"
 #define MKKV_TC_REGS_DQ "56"
 #define MKKV_TC_REGS_CTL "56"
-static_assert(8 * 112 + 16 * 56 + 4 * 56 <= 28 * 72, "register shares");
+static_assert(NTHREADS == 896 && 8 * 112 + 16 * 56 + 4 * 56 <= 28 * 72, "register shares");
 #endif
 constexpr int RAW_SLOT = ATP * HD + ATP * SCALE_ROW; // one tile of the widest format and its scales: 8704 bytes
 constexpr int NRAW = 8;
@@ -507,26 +509,31 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
             const int tbq = k_pos0 + q * ATP;
             const bool valid = q < kt.y && lane < kt.x - tbq;
             const int bits = (kv.s[side].rval && tbq >= ws) ? 8 : kv.s[side].bits;
-            // which 32-dim block of the half this lane unpacks: the four warps of a tile cover the four blocks of every row, rotated
-            // with the row so that the 16-byte loads of 8 consecutive lanes (rows 32 bits bytes apart) fall into 8 different
-            // bank groups
+            // which 32-dim blocks of a half this lane unpacks: the warps of a tile cover the four blocks of every row, rotated with
+            // the row so that the 16-byte loads of 8 consecutive lanes (rows 32 bits bytes apart) fall into 8 different bank groups
             const int jr = (c + (lane >> (bits == 6 ? 1 : (bits == 5 || bits == 7) ? 2 : 0))) & 3;
             // the packed bytes of both 128-dim halves are read first (they need no operand slot), then each half is written into its
             // slot as that slot frees up
-            const unsigned rawa = smem_u32(sm.raw[rs]), off = 4 * jr * 2048 + pos_off;
+            const unsigned rawa = smem_u32(sm.raw[rs]);
 #define MKKV_SIDE(B)                                                                                                   \
     {                                                                                                                  \
-        PackedBlock<B> b0, b1;                                                                                         \
-        dq_load<B>(b0, rawa, lane, jr, valid);                                                                         \
-        dq_load<B>(b1, rawa, lane, 4 + jr, valid);                                                                     \
+        PackedBlock<B> b0[BPW], b1[BPW];                                                                               \
+        _Pragma("unroll") for (int k = 0; k < BPW; k++) {                                                              \
+            dq_load<B>(b0[k], rawa, lane, (jr + k * (NDQ / 4)) & 3, valid);                                            \
+            dq_load<B>(b1[k], rawa, lane, 4 + ((jr + k * (NDQ / 4)) & 3), valid);                                      \
+        }                                                                                                              \
         if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.wc, a.status);                                               \
-        if (!(MKKV_ABL & 1)) dq_emit<B>(b0, smem_u32(sm.op[os]) + off);                                               \
+        if (!(MKKV_ABL & 1))                                                                                           \
+            _Pragma("unroll") for (int k = 0; k < BPW; k++)                                                            \
+                dq_emit<B>(b0[k], smem_u32(sm.op[os]) + 4 * ((jr + k * (NDQ / 4)) & 3) * 2048 + pos_off);              \
         fence_async_smem();                                                                                            \
         __syncwarp();                                                                                                  \
         if (lane == 0) mbar_arrive(&sm.op_full[os]);                                                                   \
         if (++os == NOP) os = 0, oph ^= 1, owrap = true;                                                               \
         if (owrap) tc_wait(&sm.op_empty[os], oph ^ 1, &sm.wc, a.status);                                               \
-        if (!(MKKV_ABL & 1)) dq_emit<B>(b1, smem_u32(sm.op[os]) + off);                                               \
+        if (!(MKKV_ABL & 1))                                                                                           \
+            _Pragma("unroll") for (int k = 0; k < BPW; k++)                                                            \
+                dq_emit<B>(b1[k], smem_u32(sm.op[os]) + 4 * ((jr + k * (NDQ / 4)) & 3) * 2048 + pos_off);              \
         fence_async_smem();                                                                                            \
         __syncwarp();                                                                                                  \
         if (lane == 0) mbar_arrive(&sm.op_full[os]);                                                                   \
