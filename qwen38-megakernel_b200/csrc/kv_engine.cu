@@ -100,6 +100,16 @@ KvEngine::KvEngine(const EngineConfig & cfg) : cfg_(cfg) {
         for (int s = 0; s < cfg.layers; s++) ring_[w][s] = cfg_.win > 0 && (kvb_[w][s] != 8 || cfg.win_all);
     if (cfg_.win <= 0) cfg_.spill = false;
     MKKV_CK(cudaGetDevice(&dev_));
+    try {
+        init_device_state();
+    } catch (...) { // (a constructor that throws runs no destructor: what was made so far is released here)
+        release();
+        throw;
+    }
+}
+
+void KvEngine::init_device_state() {
+    const EngineConfig & cfg = cfg_;
     MKKV_CK(cudaStreamCreateWithFlags(&st_copy_, cudaStreamNonBlocking));
     MKKV_CK(cudaEventCreateWithFlags(&ev_compute_, cudaEventDisableTiming));
     MKKV_CK(cudaEventCreateWithFlags(&ev_copy_, cudaEventDisableTiming));
@@ -178,7 +188,9 @@ void KvEngine::launch_attention(const AttnJob * jobs_host, int njobs, int items,
     launches_ += 2;
 }
 
-KvEngine::~KvEngine() {
+KvEngine::~KvEngine() { release(); }
+
+void KvEngine::release() {
     cudaSetDevice(dev_);
     cudaDeviceSynchronize();
     free_seq(main_);
@@ -201,10 +213,11 @@ KvEngine::~KvEngine() {
     cudaFree(xmax_);
     cudaFree(tc_done_);
     cudaFree(prof_);
-    cudaFreeHost(h_status_);
-    cudaEventDestroy(ev_compute_);
-    cudaEventDestroy(ev_copy_);
-    cudaStreamDestroy(st_copy_);
+    if (h_status_) cudaFreeHost(h_status_);
+    if (ev_compute_) cudaEventDestroy(ev_compute_);
+    if (ev_copy_) cudaEventDestroy(ev_copy_);
+    if (st_copy_) cudaStreamDestroy(st_copy_);
+    cudaGetLastError();
 }
 
 void KvEngine::use_device() const { MKKV_CK(cudaSetDevice(dev_)); }

@@ -177,6 +177,8 @@ class KvEngine {
         std::vector<size_t> ck_off;
     };
 
+    void init_device_state(); // the constructor's device part
+    void release();           // everything the engine owns (the destructor; the constructor when it fails part-way)
     Seq & seq_ref(int seq);
     const Seq & seq_ref(int seq) const;
     void alloc_seq(Seq & s, int ctx);
