@@ -14,10 +14,10 @@
 //   - one issuer thread runs tcgen05.mma on the slots as they fill (mbarrier "full" from the unpack warps, tcgen05.commit
 //     to "empty"), S^T in five tensor-memory buffers (K runs five groups ahead of V), O^T (two 128-dim halves) resident there
 //     for the whole kernel;
-//   - 8 softmax warps read S^T back (tcgen05.ld: a thread owns one position and 24 query rows), take the tile maxima,
-//     exchange the running max with the CTAs that hold the chunk's earlier groups through small global arrays (own group
-//     maxima and cumulative maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as
-//     the B operand. The accumulator is kept against a per-row reference max that moves rarely (when the running max passes
+//   - 8 softmax warps read S^T back (tcgen05.ld: a thread owns one position and 24 query rows), take the tile maxima (two
+//     groups ahead of P, so that a group's own maxima are published long before another CTA needs them), exchange the running
+//     max with the CTAs that hold the chunk's earlier groups through small global arrays (own group maxima and cumulative
+//     maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as the B operand. The accumulator is kept against a per-row reference max that moves rarely (when the running max passes
 //     it by more than 10.5): P, after its fp16 rounding, is multiplied by exp(running max - reference) and carried as an fp16
 //     high and low part (one N = 96 MMA per k-step, two 48-column accumulator blocks), so the reference's fp16 P is reproduced
 //     and no per-tile accumulator rescale is needed;
@@ -332,7 +332,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         sm.wc.poll = a.poll_rounds;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == W_ISSUE) { // tensor memory: S^T three times, O^T in two halves
+    if (warp == W_ISSUE) { // tensor memory: S^T five times, O^T in two halves
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
