@@ -26,6 +26,22 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+
+# Standard output carries the JSON line and nothing else: libraries that write to file descriptor 1 from native code (NCCL prints its
+# version banner there) are sent to standard error for the whole run, the line goes to the saved descriptor.
+_STDOUT_FD = None
+
+
+def claim_stdout():
+    global _STDOUT_FD
+    if _STDOUT_FD is None:
+        sys.stdout.flush()
+        _STDOUT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(text):
+    os.write(1 if _STDOUT_FD is None else _STDOUT_FD, (text + "\n").encode())
 for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
     if p not in sys.path:
         sys.path.insert(0, p)
@@ -150,7 +166,7 @@ def run_reference(args):
             "cpu_baseline": {"value": us, "unit": "us/layer", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": us, "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gb_per_s": algorithmic_bytes(CTX0, T_STEP) / us / 1e3}
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 def cpu_baseline_sample(seconds=12.0):
@@ -286,7 +302,7 @@ def run_split(args):
                            "layers": args.layers, "context": args.split_ctx, "kv_spec": SPEC, "kv_win": WIN},
                 "clocks": clocks}
         line.update({k: v for k, v in r.items() if k not in ("us_per_layer", "ms_per_step")})
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
@@ -374,7 +390,7 @@ def run_config3(args):
     r = measure_config3(args, args.steps, args.warmup, dist, rank, local_rank, world)
     clocks = sampler.stop()
     if rank == 0:
-        print(json.dumps({"metric": "aggregate_decode_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        emit(json.dumps({"metric": "aggregate_decode_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                           "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                           "dtype": "f16 operands / f32 accumulate over u8 packed 5/6/8-bit rows", "data": "synthetic",
                           "config": {"workload": "config3: 32 sequences, lengths log-uniform [2,000, 100,000], 1..8 tokens each per step, %d attention "
@@ -443,7 +459,7 @@ def run_config4(args):
     torch.cuda.set_device(local_rank)
     importlib.import_module("qwen38-megakernel_b200").load_library()
     r = measure_config4(args, max(args.steps, 1) if args.steps < 16 else 5)
-    print(json.dumps({"metric": "kv_restore_gb_per_s", "value": r["restore_gb_per_s"], "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "vs_baseline": None,
+    emit(json.dumps({"metric": "kv_restore_gb_per_s", "value": r["restore_gb_per_s"], "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "vs_baseline": None,
                       "data": "synthetic", "dtype": "u8 packed rows",
                       "config": {"workload": "config4: park 100,000 positions x %d layers (%0.2f GB with the rings), restore positions [0, 11,700) "
                                              "(%0.1f MB of rows), append 2,000 rows, decode 8 tokens" % (r["layers"], r["parked_gb"], r["restored_mb"]),
@@ -484,6 +500,7 @@ def main():
     ap.add_argument("--split-ctx", type=int, default=0, help="config 2b alone: one sequence of this many positions split over the GPUs")
     ap.add_argument("--config", type=int, default=2, help="2 (default): the headline decode workload; 3: 32 sequences dealt to the GPUs; 4: snapshot / restore")
     args = ap.parse_args()
+    claim_stdout()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else max(args.warmup, 1)
     if args.impl == "reference":
         return run_reference(args)
@@ -690,7 +707,7 @@ def main():
             line["cpu_baseline"] = cpu_baseline_sample()
     if rank == 0:
         line.update(side)
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 

@@ -125,6 +125,8 @@ struct Args {
     unsigned long long * xb; // same shape: row maxima of the chunk up to and including the group
     int nbmax, epoch;
     int * status;
+    float * raw_part;       // fused merge, optional: the merged but un-normalised (m, l, O) per kv head goes here instead of O
+    float2 * raw_ml;        // ([4][48][256] / [4][48]: the input of a later merge across GPUs)
     unsigned * done;        // fused merge: [kv head] count of CTAs whose partial is written, over all launches (wraps)
     unsigned done_target;   // the count that means "every CTA of the head, this launch"; done == null: separate merge launch
     unsigned long long * prof; // optional: [CTA][16 groups][20] globaltimer stamps: softmax warp 0 (0 .. 7), unpack warp 8 (8 .. 15),
@@ -850,7 +852,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
                     }
                 }
                 ok = __shfl_sync(FULL_MASK, ok, 0);
-                if (ok) merge_row(J, a.part, a.ml, (size_t) g * a.cph, 1, a.cph, g * GQ + rr / T, rr % T, lane, 0, nullptr, nullptr);
+                if (ok) merge_row(J, a.part, a.ml, (size_t) g * a.cph, 1, a.cph, g * GQ + rr / T, rr % T, lane, a.raw_part != nullptr, a.raw_part, a.raw_ml);
             }
         }
     }
@@ -939,8 +941,10 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
     a.poll_rounds = g_poll_rounds;
     cudaError_t e = tc_prepare();
     if (e != cudaSuccess) return e;
-    // the merge runs in the kernel's tail unless the caller wants the un-normalised partials (a later merge across GPUs)
-    const bool fused = done && done_seq && !raw_part && job.O;
+    // the merge runs in the kernel's tail (normalised into O, or un-normalised per kv head for a later merge across GPUs)
+    const bool fused = done && done_seq && (raw_part ? raw_ml != nullptr : job.O != nullptr);
+    a.raw_part = fused ? raw_part : nullptr;
+    a.raw_ml = fused ? raw_ml : nullptr;
     a.done = fused ? done : nullptr;
     a.done_target = fused ? (*done_seq + 1u) * (unsigned) a.cph : 0u;
     void * args[] = {&a};
@@ -976,6 +980,8 @@ cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * job
     a.status = status;
     a.done = nullptr;
     a.done_target = 0;
+    a.raw_part = nullptr;
+    a.raw_ml = nullptr;
     a.prof = nullptr;
     a.wait_hint_ns = g_wait_hint_ns;
     a.wait_rounds = g_wait_rounds;

@@ -604,15 +604,17 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
         cudaError_t e;
         if (tc)
             e = launch_attend_tc(j, num_sms_, part_, ml_, work_items_, xmax_, xmax_ + (size_t) NKV * ATT_NCH * xnb_ * AR, xnb_, ++epoch_, d_status_,
-                                 stream_, d_tasks_, nt, B, static_cast<float *>(part_out), static_cast<float2 *>(ml_out));
+                                 stream_, d_tasks_, nt, B, static_cast<float *>(part_out), static_cast<float2 *>(ml_out), nullptr, tc_done_, &tc_done_seq_);
         else
             e = launch_attend_fast(d_jobs_, &j, 1, NKV * j.nch, T, num_sms_, part_, ml_, work_items_, xmax_, std::min(xnb_, 64), ++epoch_, d_status_,
                                    nullptr, true, stream_, d_tasks_, nt, B, static_cast<float *>(part_out), static_cast<float2 *>(ml_out));
-        if (e == cudaSuccess) break;
+        if (e == cudaSuccess) {
+            launches_ += tc ? 1 : 2; // (the tensor-core kernel merges in its tail)
+            break;
+        }
         if (!tc || (e != cudaErrorNotSupported && e != cudaErrorCooperativeLaunchTooLarge)) MKKV_CK(e);
         cudaGetLastError();
     }
-    launches_ += 2;
 }
 
 void KvEngine::combine(int layer, int T, int nparts, const void * parts, const void * mls, void * O) {
