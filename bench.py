@@ -280,7 +280,7 @@ def measure_split(args, ctx0, steps, warmup, dist, rank, local_rank, world):
     nbytes = algorithmic_bytes(ctx0, T_STEP)
     return {"us_per_layer": us_layer, "ms_per_step": ms / steps, "context": ctx0, "layers": layers, "steps": steps, "n_gpus": world,
             "hbm_gbs_whole_job": nbytes / (us_layer * 1e-6) / 1e9, "frac_of_measured_peak_per_gpu": nbytes / (us_layer * 1e-6) / 1e9 / peak / world,
-            "combine_bytes_per_rank_step": layers * 4 * 48 * 258 * 4, "collectives_per_step": 2 if world > 1 else 0,
+            "combine_bytes_per_rank_step": layers * 4 * 48 * 258 * 4, "collectives_per_step": 1 if world > 1 else 0,
             "gpu_launches": int(launches), "output_absmax": check}
 
 

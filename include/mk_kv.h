@@ -97,6 +97,10 @@ int mk_kv_combine(void * h, int layer, int T, int nparts, const void * parts, co
 int mk_kv_step_layers_partial(void * h, int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, size_t kv_stride,
                               size_t q_stride, int own_lo, int own_hi, int pos_lo, int pos_hi, void * parts, void * mls);
 int mk_kv_combine_layers(void * h, int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride);
+/* The same merge when every rank sends ONE buffer holding its parts array and its mls array (one all-gather per decode step): rank p's
+ * arrays start p * rank_stride bytes after parts and after mls (rank_stride a multiple of 8). */
+int mk_kv_combine_layers_strided(void * h, int nlayers, int T, int nparts, const void * parts, const void * mls, size_t rank_stride, void * O,
+                                 size_t o_stride);
 /* append + attend of one decode step's layer, as the reference's attention phase does in one pass */
 int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O);
 /* One decode step over layers 0 .. nlayers - 1 in one call: layer l appends T rows at n from K + l kv_stride, V + l kv_stride

@@ -184,6 +184,13 @@ int mk_kv_combine_layers(void * hp, int nlayers, int T, int nparts, const void *
         return 0;
     });
 }
+int mk_kv_combine_layers_strided(void * hp, int nlayers, int T, int nparts, const void * parts, const void * mls, size_t rank_stride, void * O,
+                                 size_t o_stride) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->combine_layers(nlayers, T, nparts, parts, mls, O, o_stride, rank_stride);
+        return 0;
+    });
+}
 int mk_kv_attend_static(void * hp, int seq, int layer, int n, int T, const void * Q, void * O) {
     return guarded(hp, [&](KvEngine * e) {
         e->attend_static(seq, layer, n, T, Q, O);

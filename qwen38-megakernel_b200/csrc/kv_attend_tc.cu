@@ -852,7 +852,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
                     }
                 }
                 ok = __shfl_sync(FULL_MASK, ok, 0);
-                if (ok) merge_row(J, a.part, a.ml, (size_t) g * a.cph, 1, a.cph, g * GQ + rr / T, rr % T, lane, a.raw_part != nullptr, a.raw_part, a.raw_ml);
+                if (ok) merge_row(J, a.part, a.ml, (size_t) g * a.cph, (size_t) AR * HD, (size_t) AR, a.cph, g * GQ + rr / T, rr % T, lane, a.raw_part != nullptr, a.raw_part, a.raw_ml);
             }
         }
     }

@@ -514,6 +514,7 @@ AttnJob KvEngine::whole_job(const Seq & s, const char * what, int layer, int n, 
     j.pos_lo = 0;
     j.pos_hi = n + T;
     j.pstride = 1;
+    j.rstride = 0;
     // positions >= ws are read from the ring, which holds the newest rc rows written: an attend at an earlier n after rows far
     // beyond it were appended would read later positions' rows
     if (rc_ > 0 && (j.kv.s[0].rval || j.kv.s[1].rval) && s.kv_top > j.ws + rc_)
@@ -570,6 +571,7 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
     j.pos_lo = pos_lo;
     j.pos_hi = pos_hi;
     j.pstride = 1;
+    j.rstride = 0;
     if (pos_hi > pos_lo) spill_to(s, layer, std::min(j.ws, pos_hi)); // rows of this range that left the window
     std::vector<AttnTask> tasks;
     bool tc = use_tc_;
@@ -633,6 +635,7 @@ void KvEngine::combine(int layer, int T, int nparts, const void * parts, const v
     j.item0 = 0;
     j.pos_lo = j.pos_hi = 0;
     j.pstride = NKV; // partial p of kv head g is slot p * 4 + g
+    j.rstride = 0;
     MKKV_CK(launch_merge(nullptr, &j, 1, T, const_cast<float *>(static_cast<const float *>(parts)),
                          const_cast<float2 *>(static_cast<const float2 *>(mls)), stream_));
     launches_ += 1;
@@ -657,11 +660,13 @@ void KvEngine::step_layers_partial(int seq, int nlayers, int n, int T, const voi
 }
 
 // The merge of every layer's partials in one launch: parts [nparts][nlayers][4][48][256], mls [nparts][nlayers][4][48][2] (the ranks'
-// step_layers_partial outputs gathered in rank order); layer l's output goes to O + l * o_stride bytes.
-void KvEngine::combine_layers(int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride) {
+// step_layers_partial outputs gathered in rank order); layer l's output goes to O + l * o_stride bytes. rank_stride != 0: rank p's
+// two arrays start rank_stride * p bytes after parts and mls (each rank's arrays packed into one exchange buffer).
+void KvEngine::combine_layers(int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride, size_t rank_stride) {
     use_device();
     if (nlayers < 1 || nlayers > cfg_.layers || T < 1 || T > MAXT || nparts < 1 || nparts > 64 || !parts || !mls || !O)
         throw std::runtime_error("combine_layers: bad arguments");
+    if (rank_stride % 8) throw std::runtime_error("combine_layers: the stride between the ranks' arrays must be a multiple of 8 bytes");
     ensure_work(work_items_, nlayers);
     MKKV_CK(cudaEventSynchronize(ev_compute_)); // the previous upload of the job table has been consumed
     for (int l = 0; l < nlayers; l++) {
@@ -677,6 +682,7 @@ void KvEngine::combine_layers(int nlayers, int T, int nparts, const void * parts
         j.item0 = l * NKV;          // partial p of kv head g of layer l is slot (p * nlayers + l) * 4 + g
         j.pos_lo = j.pos_hi = 0;
         j.pstride = nlayers * NKV;
+        j.rstride = (long long) (rank_stride / 4); // (0: the ranks' arrays lie one after another)
     }
     MKKV_CK(cudaMemcpyAsync(d_jobs_, h_jobs_, sizeof(AttnJob) * nlayers, cudaMemcpyHostToDevice, stream_));
     MKKV_CK(cudaEventRecord(ev_compute_, stream_));

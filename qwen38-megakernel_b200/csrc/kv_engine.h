@@ -88,7 +88,7 @@ class KvEngine {
     // the same for every layer of one decode step in one call each (one collective per step between them)
     void step_layers_partial(int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, size_t kv_stride, size_t q_stride,
                              int own_lo, int own_hi, int pos_lo, int pos_hi, void * parts, void * mls);
-    void combine_layers(int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride);
+    void combine_layers(int nlayers, int T, int nparts, const void * parts, const void * mls, void * O, size_t o_stride, size_t rank_stride = 0);
     // attend() with the split partials in the library's fixed device array: this call allocates nothing
     void attend_static(int seq, int layer, int n, int T, const void * Q, void * O);
     // one launch sequence for several sequences: job j appends T[j] rows at n[j] and attends; packed device buffers in job order

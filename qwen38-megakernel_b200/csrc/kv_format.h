@@ -79,6 +79,8 @@ struct AttnJob {
     int item0;          // first (kv head, chunk) item of this job in the call's partial buffers
     int pos_lo, pos_hi; // only positions in [pos_lo, pos_hi) are attended (multiples of 32 or the context end; whole context: 0, n + T)
     int pstride;        // merge: partial c of kv head g is slot item0 + g nch + c (pstride 1), else item0 + c pstride + g
+    long long rstride;  // merge, pstride > 1 only: floats between partial c and c + 1 of both arrays when they are not pstride
+                        // slots apart (each GPU's arrays packed into one exchange buffer); 0: pstride slots
 };
 
 // one batch of tiles of one chunk, as the fast attention kernel runs it (built on the host for position-range jobs)

@@ -203,7 +203,9 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__
     const size_t i0 = (size_t) J.item0 + (J.pstride > 1 ? (size_t) g : (size_t) g * J.nch);
     const size_t cstep = J.pstride > 1 ? (size_t) J.pstride : 1; // slots between consecutive partials of the kv head
     // (partials beyond 64 per kv head do not occur: nch <= 20, or #SM / 4 for the spread kernels)
-    merge_row(J, a.part, a.ml, i0, cstep, J.nch, h, t, lane, raw, part_out, ml_out);
+    const bool packed = J.pstride > 1 && J.rstride != 0;
+    merge_row(J, a.part, a.ml, i0, packed ? (size_t) J.rstride : cstep * AR * HD, packed ? (size_t) J.rstride / 2 : cstep * AR, J.nch, h, t, lane, raw, part_out,
+              ml_out);
 }
 
 cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,

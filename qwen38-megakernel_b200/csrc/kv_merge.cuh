@@ -12,12 +12,13 @@ namespace mkkv {
 // (count of them, at most 64) of part [slot][48][256] / ml [slot][48], row r = (head % 6) T + t.
 // raw != 0: write the merged but un-normalised (m, l, O) of the row instead, as one partial per kv head (slot g of part_out /
 // ml_out): the input of a later merge across GPUs
-__device__ __forceinline__ void merge_row(const AttnJob & J, const float * part, const float2 * ml, size_t i0, size_t cstep, int count, int h,
-                                          int t, int lane, int raw, float * part_out, float2 * ml_out) {
+// pstep / mstep: floats / (m, l) pairs between consecutive partials of the row in part / ml
+__device__ __forceinline__ void merge_row(const AttnJob & J, const float * part, const float2 * ml, size_t i0, size_t pstep, size_t mstep, int count,
+                                          int h, int t, int lane, int raw, float * part_out, float2 * ml_out) {
     const int g = h / GQ, r = (h % GQ) * J.T + t;
     // lane c (and c + 32) holds partial c's (m, l): all weights first, so the sums below run over independent loads
-    float2 mla = lane < count ? __ldcg(&ml[(i0 + lane * cstep) * AR + r]) : make_float2(-CUDART_INF_F, 0.f);
-    float2 mlb = lane + 32 < count ? __ldcg(&ml[(i0 + (lane + 32) * cstep) * AR + r]) : make_float2(-CUDART_INF_F, 0.f);
+    float2 mla = lane < count ? __ldcg(&ml[i0 * AR + r + lane * mstep]) : make_float2(-CUDART_INF_F, 0.f);
+    float2 mlb = lane + 32 < count ? __ldcg(&ml[i0 * AR + r + (lane + 32) * mstep]) : make_float2(-CUDART_INF_F, 0.f);
     float M = fmaxf(mla.x, mlb.x);
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) M = fmaxf(M, __shfl_xor_sync(FULL, M, m));
@@ -29,7 +30,7 @@ __device__ __forceinline__ void merge_row(const AttnJob & J, const float * part,
 #pragma unroll 4
     for (int c = 0; c < count; c++) {
         const float w = __shfl_sync(FULL, c < 32 ? wa : wb, c & 31), lc = __shfl_sync(FULL, c < 32 ? mla.y : mlb.y, c & 31);
-        const float4 * o = reinterpret_cast<const float4 *>(pbase + (size_t) c * cstep * AR * HD);
+        const float4 * o = reinterpret_cast<const float4 *>(pbase + (size_t) c * pstep);
         const float4 o0 = __ldcg(o), o1 = __ldcg(o + 1);
         num[0] = __fmaf_rn(w, o0.x, num[0]);
         num[1] = __fmaf_rn(w, o0.y, num[1]);

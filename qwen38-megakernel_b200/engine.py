@@ -54,6 +54,7 @@ def load_library():
         "mk_kv_combine": (i, [vp, i, i, i, vp, vp, vp]),
         "mk_kv_step_layers_partial": (i, [vp, i, i, i, i, vp, vp, vp, C.c_size_t, C.c_size_t, i, i, i, i, vp, vp]),
         "mk_kv_combine_layers": (i, [vp, i, i, i, vp, vp, vp, C.c_size_t]),
+        "mk_kv_combine_layers_strided": (i, [vp, i, i, i, vp, vp, C.c_size_t, vp, C.c_size_t]),
         "mk_kv_step": (i, [vp, i, i, i, i, vp, vp, vp, vp]),
         "mk_kv_step_layers": (i, [vp, i, i, i, i, vp, vp, vp, vp, C.c_size_t, C.c_size_t, C.c_size_t]),
         "mk_kv_reserve_batch": (i, [vp, i]),
@@ -231,6 +232,12 @@ class Engine:
         """parts [nparts][layers][4][48][256], mls [nparts][layers][4][48][2] -> O [layers][T][24][256]"""
         self._ck(self.L.mk_kv_combine_layers(self.h, O.shape[0], T, nparts, _ptr(parts), _ptr(mls), _ptr(O[0]), O.stride(0) * O.element_size()),
                  "combine_layers")
+
+    def combine_layers_strided(self, T, nparts, parts, mls, rank_stride, O):
+        """combine_layers when every rank's parts and mls arrays sit in one exchange buffer: parts / mls point at rank 0's arrays, rank p's
+        start p * rank_stride bytes later"""
+        self._ck(self.L.mk_kv_combine_layers_strided(self.h, O.shape[0], T, nparts, _ptr(parts), _ptr(mls), rank_stride, _ptr(O[0]),
+                                                     O.stride(0) * O.element_size()), "combine_layers_strided")
 
     def step(self, layer, n, K, V, Q, O, seq=SEQ_MAIN):
         self._ck(self.L.mk_kv_step(self.h, seq, layer, n, Q.shape[0], _ptr(K), _ptr(V), _ptr(Q), _ptr(O)), "step")

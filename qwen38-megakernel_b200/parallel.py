@@ -118,28 +118,27 @@ class SplitSequence:
     def step(self, n, K, V, Q, O):
         """One decode step over every layer with ONE exchange: K, V [layers][T][4][256], Q [layers][T][24][256] (replicated on
         every rank), O [layers][T][24][256] fp32. Every rank appends the rows it owns and attends over its own positions for all
-        layers (one library call), the ranks' partials are all-gathered once per step (outputs and (max, sum) pairs: two small
-        collectives, 3.2 MB in all at 16 layers and 8 tokens), and one launch merges every layer."""
+        layers (one library call) into one send buffer (the outputs, then the (max, sum) pairs: 3.2 MB at 16 layers), the ranks'
+        buffers are all-gathered once per step, and one launch merges every layer."""
         import torch
         layers, T = Q.shape[0], Q.shape[1]
         L = n + T
         key = (layers, str(Q.device))
         if getattr(self, "_step_key", None) != key:
             dev = Q.device
-            self._step_bufs = (torch.empty((layers, NKV, AR, HD), dtype=torch.float32, device=dev),
-                               torch.empty((layers, NKV, AR, 2), dtype=torch.float32, device=dev),
-                               torch.empty((self.world, layers, NKV, AR, HD), dtype=torch.float32, device=dev),
-                               torch.empty((self.world, layers, NKV, AR, 2), dtype=torch.float32, device=dev))
+            npart, nml = layers * NKV * AR * HD, layers * NKV * AR * 2
+            send = torch.empty(npart + nml, dtype=torch.float32, device=dev)
+            recv = torch.empty((self.world, npart + nml), dtype=torch.float32, device=dev)
+            self._step_bufs = (send, recv, npart)
             self._step_key = key
-        part, ml, parts, mls = self._step_bufs
+        send, recv, npart = self._step_bufs
+        part, ml = send[:npart], send[npart:]
         self.eng.step_layers_partial(n, K, V, Q, self.lo, self.hi, self.lo, max(min(self.hi, L), self.lo), part, ml)
         if self.dist is not None and self.world > 1:
-            self.dist.all_gather_into_tensor(parts, part)
-            self.dist.all_gather_into_tensor(mls, ml)
+            self.dist.all_gather_into_tensor(recv, send)
         else:
-            parts[0].copy_(part)
-            mls[0].copy_(ml)
-        self.eng.combine_layers(T, self.world, parts, mls, O)
+            recv[0].copy_(send)
+        self.eng.combine_layers_strided(T, self.world, recv[0, :npart], recv[0, npart:], recv.stride(0) * 4, O)
 
     def close(self):
         self.eng.close()

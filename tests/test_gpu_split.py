@@ -92,6 +92,29 @@ def test_split_step_all_layers_one_exchange(mk, torch_cuda):
     for l in range(NL):
         assert np.isfinite(O[l]).all()
         assert np.abs(O[l] - orc.attend(l, n, Q[l])).max() <= 2e-3
+    # the packed form SplitSequence.step uses: every rank's two arrays in one buffer (one all-gather), ranks a fixed stride apart
+    npart, nml = NL * 4 * 48 * 256, NL * 4 * 48 * 2
+    packed = torch.zeros((G, npart + nml), dtype=torch.float32, device="cuda")
+    for r in range(G):
+        packed[r, :npart] = parts[r].reshape(-1)
+        packed[r, npart:] = mls[r].reshape(-1)
+    O2 = torch.empty((NL, T, 24, 256), dtype=torch.float32, device="cuda")
+    seqs[0].eng.combine_layers_strided(T, G, packed[0, :npart], packed[0, npart:], packed.stride(0) * 4, O2)
+    seqs[0].eng.sync()
+    assert np.array_equal(O2.cpu().numpy(), O)
+    # and SplitSequence.step itself with one rank (no process group): the whole range, one call
+    one = mk.parallel.SplitSequence(mk.Engine, NL, cap, spec, win, 0, 1)
+    for l in range(NL):
+        for a in range(0, n, 2048):
+            m = min(2048, n - a)
+            Kc, Vc = kvdata.kv_rows(L + l, l, a, m)
+            one.append(l, a, torch.from_numpy(Kc).cuda(), torch.from_numpy(Vc).cuda())
+    O3 = torch.empty((NL, T, 24, 256), dtype=torch.float32, device="cuda")
+    one.step(n, Kd, Vd, Qd, O3)
+    one.eng.sync()
+    for l in range(NL):
+        assert np.abs(O3[l].cpu().numpy() - orc.attend(l, n, Q[l])).max() <= 2e-3
+    one.close()
     # the step's rows landed on their owner only, with the oracle's bytes
     own = [s for s in seqs if s.lo <= n < s.hi][0]
     a, sa = own.eng.read_row(1, 0, 3, n)
