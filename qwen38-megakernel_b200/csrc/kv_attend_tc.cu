@@ -104,12 +104,12 @@ struct Smem {
                                 // groups exist or are being written, and a warp is never a whole group ahead of its slice.
                                 // The first buffer holds the row sums at the end.
     WarpScratch ws[NSOFT];
-    unsigned char rtok[AR];     // token of a query row
     unsigned tmem_base;
+    int merge_ok;               // the tail's merge: the head's CTAs have all arrived
     WaitCtl wc;                 // the launch's wait limits; dead: a wait of this CTA gave up, no later wait blocks
     AttnTask tasks[NTASK];      // the CTA's groups as the producer reaches them, by group % NTASK (no role is that far from it:
                                 // the producer's K is at most NSB + 2 groups ahead of the softmax warps' group)
-    uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[NSB], s_empty[NSB], p_full, p_empty, fin;
+    uint64_t raw_full[NRAW], raw_empty[NRAW], op_full[NOP], op_empty[NOP], s_full[NSB], s_empty[NSB], p_full, p_empty, q_ready, fin;
     AttnJob job;
 };
 
@@ -310,6 +310,9 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem & sm = *reinterpret_cast<Smem *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#if MKKV_TC_PROF
+    const unsigned long long t_entry = globaltimer_ns();
+#endif
     {
         const AttnJob * Jp = &a.one;
         if (a.jobs) { // batch mode: the job whose items contain this CTA
@@ -328,6 +331,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         mbar_init(&sm.p_full, NSOFT);
         mbar_init(&sm.p_empty, 1);
         mbar_init(&sm.fin, 1);
+        mbar_init(&sm.q_ready, NTHREADS / 32 - 1);
         sm.wc.dead = 0;
         sm.wc.hint = a.wait_hint_ns;
         sm.wc.rounds = a.wait_rounds;
@@ -337,8 +341,11 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
     if (warp == W_ISSUE) { // tensor memory: S^T five times, O^T in two halves
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tc_fence_before();
     }
     __syncthreads();
+    tc_fence_after();
+    const unsigned tb = sm.tmem_base;
     const AttnJob & J = sm.job;
     const KvView & kv = J.kv;
     // spread mode: CTA kk of kv head g runs tasks kk, kk + cph, .. of the head; batch mode: the CTA runs the groups of chunk c_fixed
@@ -358,33 +365,46 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
     const int G = kk < t_end ? (t_end - kk + tstep - 1) / tstep : 0; // this CTA's groups: tasks kk, kk + tstep, ..
 
     // query rows of the kv head: fp16 -> fp32 -> (K's rotation) -> x 1/16 -> fp16 (qwen38_mk.cu:2876-2883), row = (head % 6) T + t,
-    // as the K-major B operand: lane holds dims 8 lane .. + 7 = one 16-byte unit
-    for (int r = warp; r < AR; r += NTHREADS / 32) {
-        uint4 out = make_uint4(0, 0, 0, 0);
-        if (r < R) {
-            const uint4 rawq = *reinterpret_cast<const uint4 *>(J.Q + ((size_t) (r % T) * NH + g * GQ + r / T) * HD + lane * 8);
-            const __half2 * hh = reinterpret_cast<const __half2 *>(&rawq);
-            float v[8];
+    // as the K-major B operand: lane holds dims 8 lane .. + 7 = one 16-byte unit. Every warp but the producer stages its share at
+    // once (the producer goes straight to its copies, so the first packed tiles are on their way meanwhile); the issuer waits for
+    // all of them.
+    auto stage_q = [&]() {
+        constexpr int NQW = NTHREADS / 32 - 1;
+        const int qw = warp < W_PROD ? warp : warp - 1;
+        uint4 rawq[(AR + NQW - 1) / NQW];
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const float2 f = __half22float2(hh[k]);
-                v[2 * k] = f.x;
-                v[2 * k + 1] = f.y;
-            }
-            if (kv.s[0].rot) fwht256(v, lane);
-            __half2 * h = reinterpret_cast<__half2 *>(&out);
-#pragma unroll
-            for (int k = 0; k < 4; k++) // the unit's dims in the order the unpack warps leave K's (unit_perm)
-                h[k] = __floats2half2_rn(__fmul_rn(v[unit_perm(2 * k)], 0.0625f), __fmul_rn(v[unit_perm(2 * k + 1)], 0.0625f));
+        for (int i = 0; i < (AR + NQW - 1) / NQW; i++) { // (all of the warp's rows are requested before the first is used)
+            const int r = qw + i * NQW;
+            rawq[i] = make_uint4(0, 0, 0, 0);
+            if (r < R) rawq[i] = *reinterpret_cast<const uint4 *>(J.Q + ((size_t) (r % T) * NH + g * GQ + r / T) * HD + lane * 8);
         }
-        *reinterpret_cast<uint4 *>(sm.q + lane * (AR / 8 * 128) + (r >> 3) * 128 + (r & 7) * 16) = out;
-    }
-    if (tid < AR) sm.rtok[tid] = (unsigned char) (tid % T);
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const unsigned tb = sm.tmem_base;
+#pragma unroll
+        for (int i = 0; i < (AR + NQW - 1) / NQW; i++) {
+            const int r = qw + i * NQW;
+            if (r >= AR) break;
+            uint4 out = make_uint4(0, 0, 0, 0);
+            if (r < R) {
+                const __half2 * hh = reinterpret_cast<const __half2 *>(&rawq[i]);
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float2 f = __half22float2(hh[k]);
+                    v[2 * k] = f.x;
+                    v[2 * k + 1] = f.y;
+                }
+                if (kv.s[0].rot) fwht256(v, lane);
+                __half2 * h = reinterpret_cast<__half2 *>(&out);
+#pragma unroll
+                for (int k = 0; k < 4; k++) // the unit's dims in the order the unpack warps leave K's (unit_perm)
+                    h[k] = __floats2half2_rn(__fmul_rn(v[unit_perm(2 * k)], 0.0625f), __fmul_rn(v[unit_perm(2 * k + 1)], 0.0625f));
+            }
+            *reinterpret_cast<uint4 *>(sm.q + lane * (AR / 8 * 128) + (r >> 3) * 128 + (r & 7) * 16) = out;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.q_ready);
+    };
+    if (warp != W_PROD) stage_q(); // (one copy of that code, before the roles part; the producer is already fetching)
     // registers move from the unpack / control warps to the softmax warps
     if (warp >= W_ISSUE) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 " MKKV_TC_REGS_CTL ";");
@@ -434,6 +454,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         // ---- issuer: S(0) .. S(NSB - 1), then PV(i), S(i + NSB) ----
         if (lane == 0) {
             unsigned oseq = 0;
+            tc_wait(&sm.q_ready, 0u, &sm.wc, a.status); // the queries are staged
             const unsigned q_lo = desc_lo(smem_u32(sm.q), AR / 8 * 128), p_lo0 = desc_lo(smem_u32(sm.p[0]), 128);
             const unsigned hi_k = desc_hi(128), hi_mn = desc_hi(2048); // K-major: 8-row groups 128 bytes apart; MN-major: 2048
             for (int nk = 0, nv = 0; nv < G && !sm.wc.dead;) {
@@ -558,6 +579,9 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 " MKKV_TC_REGS_SOFT ";");
+#if MKKV_TC_PROF
+        const unsigned long long t_loop = globaltimer_ns();
+#endif
         // ---- softmax warps: warp = 4 c2 + q: positions 32 q .. + 31 of a group (tensor-memory lanes 32 q ..), query rows
         // 24 c2 .. + 23. Lanes 0 .. 23 own one row each (its running / reference max; replicated over the four q) ----
         const int q = warp & 3, c2 = warp >> 2, prow = ATP * q + lane, row0 = RS * c2;
@@ -584,7 +608,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
 #pragma unroll 1
                 for (int i = 0; i < RS; i++) {
                     const int r = row0 + i;
-                    if (p_abs > min(k.c1 - 1, n + (int) sm.rtok[r]) || r >= R) m |= 1u << i;
+                    if (p_abs > min(k.c1 - 1, n + r % T) || r >= R) m |= 1u << i;
                 }
             }
             return m;
@@ -780,24 +804,38 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         };
 
         if (G > 0) {
-            // maxima of group i + MAX_AHEAD, then P of group i (tasks: left by the producer, see there). The maxima run two groups
-            // ahead of P so that a group's own maxima are published well before the CTAs that hold the chunk's next groups need
-            // them: the CTAs of a kv head may drift apart by a group without a poll having to wait
+            // Tile maxima run ahead of P (tasks: left by the producer, see there), so that a group's own maxima are published well
+            // before the CTAs that hold the chunk's next groups need them: the CTAs of a kv head may drift apart by a group
+            // without a poll having to wait. The lead grows from none (the first P needs only its own group's scores) to two groups.
             constexpr int MAX_AHEAD = 2;
-            for (int i = -MAX_AHEAD; i < G; i++) {
-                if (i + MAX_AHEAD < G) maxima(i + MAX_AHEAD);
-                if (i >= 0) {
-                    const Task kc = sm.tasks[i % NTASK];
-                    softmax(i, kc);
-                }
-                if (i + 1 >= 0 && i + 1 < G) {
+            int maxima_done = 0;
+            for (int i = 0; i < G; i++) {
+                const int want = min(G, i + 1 + min(i, MAX_AHEAD));
+                while (maxima_done < want) maxima(maxima_done++);
+                const Task kc = sm.tasks[i % NTASK];
+                softmax(i, kc);
+                if (i + 1 < maxima_done) { // (the next group's task record is known to be written: its scores have been waited for)
                     const Task kn = sm.tasks[(i + 1) % NTASK];
                     request_words(kn);
+                } else {
+                    w0 = w1 = w2 = 0ull; // (no early request: the polls fetch the words themselves)
                 }
             }
             tc_wait(&sm.p_empty, (G - 1) & 1, &sm.wc, a.status);
             tc_fence_after();
         }
+#if MKKV_TC_PROF
+        if (warp == 0) { // the tail's stamps go to group slot 15 (stamps 8 .. 13, after the main loop's own use of them)
+            if (a.prof && lane == 0) {
+                a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 8] = t_entry;
+                a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 9] = t_loop;
+                unsigned smid;
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 14] = smid; // (which SM ran this CTA)
+            }
+            TC_STAMP(15, 10);
+        }
+#endif
         // ---- the CTA's partial: O^T lanes are dims (in the unpacked units' order: mapped back here), columns are query rows ----
         const int pdim = (prow & ~7) | unit_perm(prow & 7);
 #pragma unroll
@@ -831,16 +869,19 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         named_bar(5, NSOFT * 32);
         if (owner && q == 0 && r_own < R)
             a.ml[(size_t) slot * AR + r_own] = make_float2(m_acc, lsum[0][r_own] + lsum[1][r_own] + lsum[2][r_own] + lsum[3][r_own]);
+#if MKKV_TC_PROF
+        if (warp == 0) TC_STAMP(15, 11);
+#endif
         if (a.done) {
             // ---- the merge, in the kernel's tail: when every CTA of the kv head has written its partial, this CTA merges rows
-            // kk, kk + cph of the head's 6 T (one warp per row, as attn_merge_kernel) ----
+            // kk and kk + cph of the head's 6 T. Four warps share a row (warp j of the team: partials j, j + 4, ..: all their loads
+            // are in flight at once), the team's sums meet in shared memory (an operand slot: every MMA of the CTA is complete) ----
             __threadfence();
             named_bar(5, NSOFT * 32);
-            if (warp == 0 && lane == 0) atomicAdd(a.done + g, 1u);
-            const int rr = kk + warp * a.cph;
-            if (warp < 2 && rr < GQ * T) {
+            if (warp == 0) {
                 bool ok = true;
                 if (lane == 0) {
+                    atomicAdd(a.done + g, 1u);
                     unsigned it = 0;
                     while ((int) (ld_acquire_u32(a.done + g) - a.done_target) < 0) {
                         __nanosleep(100);
@@ -850,10 +891,39 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
                             break;
                         }
                     }
+                    sm.merge_ok = ok;
                 }
-                ok = __shfl_sync(FULL_MASK, ok, 0);
-                if (ok) merge_row(J, a.part, a.ml, (size_t) g * a.cph, (size_t) AR * HD, (size_t) AR, a.cph, g * GQ + rr / T, rr % T, lane, a.raw_part != nullptr, a.raw_part, a.raw_ml);
             }
+            named_bar(5, NSOFT * 32);
+#if MKKV_TC_PROF
+            if (warp == 0) TC_STAMP(15, 12);
+#endif
+            const int team = warp >> 2, tj = warp & 3, rr = kk + team * a.cph;
+            const bool has = sm.merge_ok && rr < GQ * T;
+            float * const scratch = reinterpret_cast<float *>(sm.op[0]); // [warp][lane][8 sums], then [warp] weights' sums
+            float num[8], den = 0.f, M = -CUDART_INF_F;
+            if (has) {
+                merge_accumulate(a.part, a.ml, (size_t) g * a.cph, (size_t) AR * HD, (size_t) AR, a.cph, tj, 4, rr, lane, num, den, M);
+                float4 * d = reinterpret_cast<float4 *>(scratch + ((size_t) warp * 32 + lane) * 8);
+                d[0] = make_float4(num[0], num[1], num[2], num[3]);
+                d[1] = make_float4(num[4], num[5], num[6], num[7]);
+                if (lane == 0) scratch[NSOFT * 32 * 8 + warp] = den;
+            }
+            named_bar(5, NSOFT * 32);
+            if (has && tj == 0) {
+#pragma unroll
+                for (int w2 = 1; w2 < 4; w2++) {
+                    const float4 * o = reinterpret_cast<const float4 *>(scratch + ((size_t) (warp + w2) * 32 + lane) * 8);
+                    const float4 o0 = o[0], o1 = o[1];
+                    num[0] += o0.x, num[1] += o0.y, num[2] += o0.z, num[3] += o0.w;
+                    num[4] += o1.x, num[5] += o1.y, num[6] += o1.z, num[7] += o1.w;
+                    den += scratch[NSOFT * 32 * 8 + warp + w2];
+                }
+                merge_finish(J, g * GQ + rr / T, rr % T, lane, a.raw_part != nullptr, a.raw_part, a.raw_ml, num, den, M);
+            }
+#if MKKV_TC_PROF
+            if (warp == 0) TC_STAMP(15, 13);
+#endif
         }
     }
     tc_fence_before();
