@@ -601,14 +601,20 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         auto exch_ok = [&](const Task & k) -> bool { return !sm.wc.dead && (unsigned) k.c < (unsigned) ATT_NCH && (unsigned) k.b < (unsigned) a.nbmax; };
         // which of the warp's rows this thread's position must not see in group k: row token t sees positions <= n + t; positions
         // past the chunk end and padding rows see nothing (0 for almost every group: uniform test first)
+        unsigned pad_mask = 0u; // the warp's rows beyond the job's 6 T (fewer than 8 tokens): never visible
+#pragma unroll
+        for (int i = 0; i < RS; i++)
+            if (row0 + i >= R) pad_mask |= 1u << i;
+        const int tok0 = row0 % T; // token of the warp's first row (row = (head % 6) T + t)
         auto row_mask = [&](const Task & k) -> unsigned {
-            unsigned m = 0u;
-            if (k.pos0 + GP - 1 > min(k.c1 - 1, n) || R < AR) {
+            unsigned m = pad_mask;
+            if (k.pos0 + GP - 1 > min(k.c1 - 1, n)) { // (the group reaches the chunk's end or the new tokens: the last groups only)
                 const int p_abs = k.pos0 + prow;
+                int t = tok0;
 #pragma unroll 1
                 for (int i = 0; i < RS; i++) {
-                    const int r = row0 + i;
-                    if (p_abs > min(k.c1 - 1, n + r % T) || r >= R) m |= 1u << i;
+                    if (p_abs > min(k.c1 - 1, n + t)) m |= 1u << i;
+                    if (++t == T) t = 0;
                 }
             }
             return m;
