@@ -782,17 +782,28 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
 #if MKKV_TC_PROF
             if (anyf && a.prof && st && lane == 0) a.prof[((size_t) blockIdx.x * 16 + 15) * 20 + 15] += 1ull | ((unsigned long long) __popc(anyf) << 32);
 #endif
-            if (anyf) { // bring this warp's block of the accumulator to the moved reference max
+            if (anyf) { // bring the accumulator columns of the rows whose reference max moved (one, as a rule) to the new reference:
+                        // a row is one column in each of the four blocks (two halves x high / low part); the four loads of a row
+                        // are in flight together
+                unsigned left = anyf;
 #pragma unroll 1
-                for (int hg = 0; hg < 4 * (RS / 8); hg++) { // (half, high / low block, 8 columns)
-                    const int h = hg / (2 * (RS / 8)), pt = (hg / (RS / 8)) & 1, gq = hg % (RS / 8);
-                    if (!((anyf >> (8 * gq)) & 0xffu)) continue; // no row of these 8 moved
-                    const unsigned ad = lane_addr + (h ? O_COL1 : O_COL0) + AR * pt + row0 + 8 * gq;
-                    float v[8];
-                    tmem_ld8(ad, v);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) v[j] *= W.f[8 * gq + j];
-                    tmem_st8(ad, v);
+                while (left) {
+                    const int r = __ffs(left) - 1;
+                    left &= left - 1;
+                    const float fr = W.f[r];
+                    const unsigned ad = lane_addr + row0 + r;
+                    unsigned v0, v1, v2, v3;
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v0) : "r"(ad + O_COL0));
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v1) : "r"(ad + O_COL0 + AR));
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v2) : "r"(ad + O_COL1));
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v3) : "r"(ad + O_COL1 + AR));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(v0), "+r"(v1), "+r"(v2), "+r"(v3)::"memory");
+                    v0 = __float_as_uint(__uint_as_float(v0) * fr), v1 = __float_as_uint(__uint_as_float(v1) * fr);
+                    v2 = __float_as_uint(__uint_as_float(v2) * fr), v3 = __float_as_uint(__uint_as_float(v3) * fr);
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(ad + O_COL0), "r"(v0) : "memory");
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(ad + O_COL0 + AR), "r"(v1) : "memory");
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(ad + O_COL1), "r"(v2) : "memory");
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(ad + O_COL1 + AR), "r"(v3) : "memory");
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
