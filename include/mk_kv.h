@@ -199,6 +199,10 @@ long long mk_kv_state_digest(void * h, int seq, unsigned long long * out, long l
 int mk_kv_read_row(void * h, int seq, int layer, int side, int kv_head, int pos, int ring, void * val, void * sc);
 int mk_kv_write_row(void * h, int seq, int layer, int side, int kv_head, int pos, int ring, const void * val, const void * sc);
 /* format facts: bits of a side (0 K, 1 V) of a layer, 1 if it has a ring, ring rows per kv head, device bytes held */
+/* Diagnostic, no counterpart in the reference: the operand values the tensor-core attention kernel's unpack step makes of nrows packed
+ * rows of `bits` bits (device pointers: rows [nrows][32 bits] bytes, scales [nrows][8] fp16) -> out [nrows][256] fp16 in natural dim
+ * order; they are fp16(d * q) of qwen38_mk.cu:2335-2343,2457-2468, which the parity tests check bit for bit. */
+int mk_kv_unpack_probe(void * h, int bits, const void * rows, const void * scales, int nrows, void * out);
 int mk_kv_bits(void * h, int side, int layer);
 int mk_kv_has_ring(void * h, int side, int layer);
 int mk_kv_ring_rows(void * h);

@@ -214,37 +214,44 @@ int att_cap_T(int n, int T) {
 }
 
 // ---- MK_KV spec: loader.cu:1329-1366 ----
+// Grammar: items separated by commas, each <K|V|*><layer|*|nothing>=<4..8>[r]; a later item overrides an earlier one; every
+// side starts as 8 bits, not rotated. Errors carry the reference's messages.
 bool parse_spec(const char * spec, int layers, int (*kvb)[MAX_LAYERS], int (*rot)[MAX_LAYERS]) {
     for (int s = 0; s < MAX_LAYERS; s++) {
         kvb[0][s] = kvb[1][s] = 8;
         rot[0][s] = rot[1][s] = 0;
     }
-    const std::string str = spec ? spec : "";
-    size_t i = 0;
-    while (i < str.size()) {
-        size_t j = str.find(',', i);
-        if (j == std::string::npos) j = str.size();
-        const std::string tok = str.substr(i, j - i);
-        i = j + 1;
-        if (tok.empty()) continue;
-        const size_t e = tok.find('=');
-        if (e == std::string::npos || e == 0 || !strchr("KV*", tok[0])) { g_err = "MK_KV: bad item " + tok; return false; }
-        const std::string sl = tok.substr(1, e - 1), md = tok.substr(e + 1);
-        if (md.empty() || md.size() > 2 || md[0] < '4' || md[0] > '8' || (md.size() == 2 && md[1] != 'r')) {
-            g_err = "MK_KV: expected 4..8 or 4r..8r in " + tok;
+    const char * p = spec ? spec : "";
+    while (*p) {
+        const char * end = strchr(p, ',');
+        const std::string item = end ? std::string(p, end) : std::string(p);
+        p = end ? end + 1 : p + item.size();
+        if (item.empty()) continue;
+        // side letter, layer field, '=', format field
+        const size_t eq = item.find('=');
+        const bool side_ok = item[0] == 'K' || item[0] == 'V' || item[0] == '*';
+        if (eq == std::string::npos || eq == 0 || !side_ok) { g_err = "MK_KV: bad item " + item; return false; }
+        const std::string layer_field = item.substr(1, eq - 1), fmt = item.substr(eq + 1);
+        int bits = 0, rotated = 0;
+        if (fmt.size() >= 1 && fmt.size() <= 2 && fmt[0] >= '4' && fmt[0] <= '8' && (fmt.size() == 1 || fmt[1] == 'r')) {
+            bits = fmt[0] - '0';
+            rotated = fmt.size() == 2;
+        } else {
+            g_err = "MK_KV: expected 4..8 or 4r..8r in " + item;
             return false;
         }
-        const bool r = md.size() == 2, all = sl.empty() || sl == "*";
-        char * end = nullptr;
-        const long slot = all ? -1 : strtol(sl.c_str(), &end, 10);
-        if (!all && (*end || slot < 0 || slot >= layers)) { g_err = "MK_KV: bad slot in " + tok; return false; }
-        for (int w = 0; w < 2; w++)
-            if (tok[0] == '*' || tok[0] == "KV"[w])
-                for (int s = 0; s < layers; s++)
-                    if (all || s == slot) {
-                        kvb[w][s] = md[0] - '0';
-                        rot[w][s] = r;
-                    }
+        int lo = 0, hi = layers; // the layers the item names: all, or one
+        if (!layer_field.empty() && layer_field != "*") {
+            long v = -1;
+            if (layer_field.find_first_not_of("0123456789") == std::string::npos && layer_field.size() < 7) v = atol(layer_field.c_str());
+            if (v < 0 || v >= layers) { g_err = "MK_KV: bad slot in " + item; return false; }
+            lo = (int) v;
+            hi = lo + 1;
+        }
+        for (int l = lo; l < hi; l++) {
+            if (item[0] != 'V') kvb[0][l] = bits, rot[0][l] = rotated;
+            if (item[0] != 'K') kvb[1][l] = bits, rot[1][l] = rotated;
+        }
     }
     return true;
 }

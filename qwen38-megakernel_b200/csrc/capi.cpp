@@ -427,6 +427,12 @@ int mk_kv_write_row(void * hp, int seq, int layer, int side, int g, int pos, int
         return 0;
     });
 }
+int mk_kv_unpack_probe(void * hp, int bits, const void * rows, const void * scales, int nrows, void * out) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->unpack_probe(bits, rows, scales, nrows, out);
+        return 0;
+    });
+}
 int mk_kv_bits(void * hp, int side, int layer) {
     return guarded(hp, [&](KvEngine * e) {
         if (side < 0 || side > 1 || layer < 0 || layer >= e->config().layers) throw std::runtime_error("mk_kv_bits: out of range");

@@ -948,7 +948,51 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
     if (warp == W_ISSUE) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(TMEM_COLS) : "memory");
 }
 
+// ---- test probe of the unpack step ----
+// nrows packed rows of BITS bits (values [nrows][32 BITS] bytes, scales [nrows][8] fp16) through the very code the unpack warps run
+// (dq_load / dq_emit on a staged tile), back in natural dim order: out [nrows][256] fp16 bit patterns. One warp per 32-row tile.
+template <int BITS> __global__ void __launch_bounds__(32) unpack_probe_kernel(const uint8_t * rows, const uint16_t * sc, int nrows, uint16_t * out) {
+    __shared__ __align__(128) uint8_t raw[RAW_SLOT];
+    __shared__ __align__(128) uint8_t op[4 * 2048]; // one 32-dim block: four dim groups of 128 positions x 16 bytes
+    const int lane = threadIdx.x, row = blockIdx.x * ATP + lane;
+    const bool valid = row < nrows;
+    constexpr int RB = 32 * BITS;
+    for (int i = lane; i < ATP * RB / 4; i += 32) { // the tile as the bulk copies leave it: rows, then the scale rows
+        const int r = blockIdx.x * ATP + i / (RB / 4);
+        reinterpret_cast<unsigned *>(raw)[i] = r < nrows ? reinterpret_cast<const unsigned *>(rows)[(size_t) blockIdx.x * ATP * RB / 4 + i] : 0u;
+    }
+    for (int i = lane; i < ATP * 8; i += 32) {
+        const int r = blockIdx.x * ATP + i / 8;
+        reinterpret_cast<uint16_t *>(raw + TILE_SC_OFF)[i] = r < nrows ? sc[(size_t) blockIdx.x * ATP * 8 + i] : (uint16_t) 0;
+    }
+    __syncwarp();
+    for (int jb = 0; jb < 8; jb++) {
+        dq_item<BITS>(smem_u32(raw), lane, jb, valid, smem_u32(op) + lane * 16);
+        __syncwarp();
+        if (valid)
+            for (int u = 0; u < 4; u++) {
+                const uint16_t * unit = reinterpret_cast<const uint16_t *>(op + u * 2048 + lane * 16);
+                for (int j = 0; j < 8; j++) out[(size_t) row * HD + 32 * jb + 8 * u + unit_perm(j)] = unit[j];
+            }
+        __syncwarp();
+    }
+}
+
 } // namespace tc
+
+cudaError_t launch_unpack_probe(int bits, const uint8_t * rows, const uint16_t * sc, int nrows, uint16_t * out, cudaStream_t stream) {
+    if (nrows < 1) return cudaSuccess;
+    const int grid = (nrows + ATP - 1) / ATP;
+    switch (bits) {
+    case 4: tc::unpack_probe_kernel<4><<<grid, 32, 0, stream>>>(rows, sc, nrows, out); break;
+    case 5: tc::unpack_probe_kernel<5><<<grid, 32, 0, stream>>>(rows, sc, nrows, out); break;
+    case 6: tc::unpack_probe_kernel<6><<<grid, 32, 0, stream>>>(rows, sc, nrows, out); break;
+    case 7: tc::unpack_probe_kernel<7><<<grid, 32, 0, stream>>>(rows, sc, nrows, out); break;
+    case 8: tc::unpack_probe_kernel<8><<<grid, 32, 0, stream>>>(rows, sc, nrows, out); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
 
 static_assert(sizeof(tc::Smem) + 128 <= 232448, "shared memory of one CTA");
 size_t attend_tc_smem_bytes() { return sizeof(tc::Smem) + 128; }

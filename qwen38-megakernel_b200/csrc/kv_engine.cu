@@ -49,32 +49,55 @@ void cuda_fail(cudaError_t e, const char * what, const char * file, int line) {
 constexpr int XCH_NB_MIN = 64; // fewest batches per chunk the exchange arrays of the spread attention kernels hold
 
 namespace {
-bool parse_spec(const std::string & str, int layers, int (*kvb)[MAX_LAYERS], int (*rot)[MAX_LAYERS]) {
-    // MK_KV grammar: comma-separated <K|V|*><layer|*|empty>=<4..8>[r] (loader.cu:1329-1366)
-    size_t i = 0;
-    while (i < str.size()) {
-        size_t j = str.find(',', i);
-        if (j == std::string::npos) j = str.size();
-        const std::string tok = str.substr(i, j - i);
-        i = j + 1;
-        if (tok.empty()) continue;
-        const size_t e = tok.find('=');
-        if (e == std::string::npos || e == 0 || !strchr("KV*", tok[0])) throw std::runtime_error("MK_KV: bad item " + tok);
-        const std::string sl = tok.substr(1, e - 1), md = tok.substr(e + 1);
-        if (md.empty() || md.size() > 2 || md[0] < '4' || md[0] > '8' || (md.size() == 2 && md[1] != 'r'))
-            throw std::runtime_error("MK_KV: expected 4..8 or 4r..8r in " + tok);
-        const bool r = md.size() == 2, all = sl.empty() || sl == "*";
-        char * end = nullptr;
-        const long slot = all ? -1 : strtol(sl.c_str(), &end, 10);
-        if (!all && (*end || slot < 0 || slot >= layers))
-            throw std::runtime_error("MK_KV: bad slot in " + tok + " (0.." + std::to_string(layers - 1) + " or *)");
-        for (int w = 0; w < 2; w++)
-            if (tok[0] == '*' || tok[0] == "KV"[w])
-                for (int s = 0; s < layers; s++)
-                    if (all || s == slot) {
-                        kvb[w][s] = md[0] - '0';
-                        rot[w][s] = r;
-                    }
+// One item of the MK_KV grammar (loader.cu:1329-1366): <K|V|*><layer|*|empty>=<4..8>[r]. The messages are the reference's.
+struct SpecItem {
+    bool sides[2]; // applies to K / to V
+    int layer;     // -1: every layer
+    int bits;
+    bool rotated;
+};
+SpecItem parse_spec_item(const std::string & item, int layers) {
+    const auto bad = [&](const std::string & what) -> std::runtime_error { return std::runtime_error("MK_KV: " + what); };
+    const size_t eq = item.find('=');
+    const char side = item.empty() ? 0 : item[0];
+    if (eq == std::string::npos || eq == 0 || (side != 'K' && side != 'V' && side != '*')) throw bad("bad item " + item);
+    SpecItem it;
+    it.sides[0] = side != 'V';
+    it.sides[1] = side != 'K';
+    // the format: one digit 4 .. 8, optionally followed by r
+    const std::string fmt = item.substr(eq + 1);
+    const bool fmt_ok = (fmt.size() == 1 || (fmt.size() == 2 && fmt[1] == 'r')) && fmt[0] >= '4' && fmt[0] <= '8';
+    if (!fmt_ok) throw bad("expected 4..8 or 4r..8r in " + item);
+    it.bits = fmt[0] - '0';
+    it.rotated = fmt.size() == 2;
+    // the layer: nothing or * for all, else a decimal number below the layer count
+    const std::string which = item.substr(1, eq - 1);
+    it.layer = -1;
+    if (!which.empty() && which != "*") {
+        bool digits = true;
+        long v = 0;
+        for (char ch : which) {
+            digits = digits && ch >= '0' && ch <= '9' && v < 100000;
+            v = v * 10 + (ch - '0');
+        }
+        if (!digits || v >= layers) throw bad("bad slot in " + item + " (0.." + std::to_string(layers - 1) + " or *)");
+        it.layer = (int) v;
+    }
+    return it;
+}
+// the items apply in order, later ones override earlier ones
+bool parse_spec(const std::string & spec, int layers, int (*kvb)[MAX_LAYERS], int (*rot)[MAX_LAYERS]) {
+    for (size_t at = 0; at <= spec.size();) {
+        const size_t comma = std::min(spec.find(',', at), spec.size());
+        if (comma > at) {
+            const SpecItem it = parse_spec_item(spec.substr(at, comma - at), layers);
+            for (int w = 0; w < 2; w++)
+                for (int l = it.layer < 0 ? 0 : it.layer; it.sides[w] && l < (it.layer < 0 ? layers : it.layer + 1); l++) {
+                    kvb[w][l] = it.bits;
+                    rot[w][l] = it.rotated;
+                }
+        }
+        at = comma + 1;
     }
     return true;
 }
@@ -981,6 +1004,13 @@ size_t KvEngine::park_bytes(int id) const {
     const auto it = parked_.find(id);
     return it == parked_.end() ? 0 : it->second.blob.used;
 }
+void KvEngine::unpack_probe(int bits, const void * rows, const void * scales, int nrows, void * out) {
+    use_device();
+    if (bits < 4 || bits > 8 || nrows < 0 || (nrows && (!rows || !scales || !out))) throw std::runtime_error("unpack_probe: bad arguments");
+    MKKV_CK(launch_unpack_probe(bits, static_cast<const uint8_t *>(rows), static_cast<const uint16_t *>(scales), nrows, static_cast<uint16_t *>(out), stream_));
+    launches_++;
+}
+
 // ---- prompt-state file (state_files.cu:97-238) ----
 // The regions in the file's order: for every layer, side, kv head the values of rows 0 .. hend - 1, then their scales (:103-110);
 // then for every (layer, side) with a ring all heads' ring values, then all heads' ring scales (:115-119).

@@ -58,6 +58,8 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
 cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
                                    float2 * ml, int part_slots, int * status, cudaStream_t stream);
 size_t attend_tc_smem_bytes();
+// test probe: the tensor-core kernel's unpack step on nrows packed rows -> fp16 operand values [nrows][256] in natural dim order
+cudaError_t launch_unpack_probe(int bits, const uint8_t * rows, const uint16_t * sc, int nrows, uint16_t * out, cudaStream_t stream);
 // load every kernel of the library on the current device (no launch allocates afterwards); the engine calls it at construction
 cudaError_t preload_kernels();
 cudaError_t preload_attend_fast();

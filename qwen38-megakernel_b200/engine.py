@@ -99,6 +99,7 @@ def load_library():
         "mk_kv_state_digest": (ll, [vp, i, ullp, ll]),
         "mk_kv_read_row": (i, [vp, i, i, i, i, i, i, vp, vp]),
         "mk_kv_write_row": (i, [vp, i, i, i, i, i, i, vp, vp]),
+        "mk_kv_unpack_probe": (i, [vp, i, vp, vp, i, vp]),
         "mk_kv_bits": (i, [vp, i, i]),
         "mk_kv_has_ring": (i, [vp, i, i]),
         "mk_kv_ring_rows": (i, [vp]),
@@ -402,6 +403,10 @@ class Engine:
         val = np.ascontiguousarray(val, dtype=np.uint8)
         sc = np.ascontiguousarray(sc, dtype=np.uint16)
         self._ck(self.L.mk_kv_write_row(self.h, seq, layer, side, g, pos, int(ring), val.ctypes.data, sc.ctypes.data), "write_row")
+
+    def unpack_probe(self, bits, rows, scales, out):
+        """rows uint8 [n][32 bits], scales fp16 [n][8] -> out fp16 [n][256]: the operand values the tensor-core kernel's unpack makes"""
+        self._ck(self.L.mk_kv_unpack_probe(self.h, bits, _ptr(rows), _ptr(scales), rows.shape[0], _ptr(out)), "unpack_probe")
 
     def bits(self, side, layer):
         return self._ck(self.L.mk_kv_bits(self.h, side, layer), "bits")

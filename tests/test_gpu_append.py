@@ -180,3 +180,29 @@ def test_step_layers_equals_per_layer_steps(mk, torch_cuda):
             rb, sb = b.read_row(l, side, 2, L + T - 1)
             assert np.array_equal(ra, rb) and np.array_equal(sa, sb)
     a.close(); b.close()
+
+
+def test_per_layer_spec_items_match_oracle(mk, torch_cuda):
+    """items of the MK_KV grammar that name one layer or one side, later items overriding earlier ones (loader.cu:1329-1366): the
+    engine's formats, rotations (through the bytes) and rings equal the oracle's, layer by layer, and so do bytes and attention"""
+    torch = torch_cuda
+    spec, win, NL, L = "K*=5r,V*=6,K1=8,V0=4r,*2=7,V2=5r,K3=6", 640, 4, 1500
+    eng = mk.Engine(NL, L + 8, spec, win)
+    orc = ko.Cache(NL, L + 8, spec, win)
+    want = {(0, 0): 5, (1, 0): 4, (0, 1): 8, (1, 1): 6, (0, 2): 7, (1, 2): 5, (0, 3): 6, (1, 3): 6}
+    for (w, l), b in want.items():
+        assert eng.bits(w, l) == orc.bits(w, l) == b
+        assert eng.has_ring(w, l) == orc.has_ring(w, l) == (b != 8)
+    for layer in range(NL):
+        fill_both(torch, eng, orc, layer, 0, L, seed=20 + layer)
+        assert_rows_equal(eng, orc, layer, [0, 639, 640, L - 1], ring_positions=[L - 600, L - 1])
+    eng.commit(L)
+    assert np.array_equal(eng.state_digest(), orc.digest(L))
+    n, T = L - 4, 4
+    for layer in range(NL):
+        Q = kvdata.q_rows(9, layer, n, T)
+        O = torch.empty((T, 24, 256), dtype=torch.float32, device="cuda")
+        eng.attend(layer, n, torch.from_numpy(Q).cuda(), O)
+        eng.sync()
+        assert np.abs(O.cpu().numpy() - orc.attend(layer, n, Q)).max() <= 2e-3, layer
+    eng.close()
