@@ -579,20 +579,20 @@ def main():
     filler = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")
 
     def timed_attends(pairs):
-        """a step whose attention launches carry an event pair each; a few ms of device work is queued first so that the host is
-        ahead of the device and the pairs time device work only"""
+        """a step whose attention launches (one per layer, back to back, nothing between them) sit inside one event pair; a few ms of
+        device work is queued first so that the host is ahead of the device and the pair times device work only"""
         n = state["n"]
         T = mk.cap_T(n, T_STEP)
         for l in range(layers):
             eng.append_raw(l, n, T, Kd[l], Vd[l])
         for _ in range(6):
             filler.fill_(1)
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
         for l in range(layers):
-            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
             eng.attend(l, n, Qd[l, :T], Od[l, :T])
-            e1.record(stream)
-            pairs.append((e0, e1))
+        e1.record(stream)
+        pairs.append((e0, e1))
         advance(n, T)
 
     def barrier():
@@ -633,9 +633,9 @@ def main():
     for _ in range(min(args.steps, 8)):
         timed_attends(pairs)
     torch.cuda.synchronize()
-    att_ms = [a.elapsed_time(b) for a, b in pairs]
-    att_bytes = state["bytes"] / len(pairs)
-    att_us = 1e3 * sum(att_ms) / len(att_ms)
+    att_ms = [a.elapsed_time(b) for a, b in pairs]  # (each pair: one launch per layer)
+    att_bytes = state["bytes"] / (len(pairs) * layers)
+    att_us = 1e3 * sum(att_ms) / (len(att_ms) * layers)
     # --- end to end: host buffers in, host result out, every step ---
     one_step(host=True)
     ms_e2e, _, _ = timed_steps(True)

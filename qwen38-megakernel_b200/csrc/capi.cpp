@@ -207,11 +207,7 @@ int mk_kv_step(void * hp, int seq, int layer, int n, int T, const void * K, cons
 int mk_kv_step_layers(void * hp, int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O,
                       size_t kv_stride, size_t q_stride, size_t o_stride) {
     return guarded(hp, [&](KvEngine * e) {
-        if (nlayers < 0 || nlayers > e->config().layers) throw std::runtime_error("step_layers: nlayers must be 0.." + std::to_string(e->config().layers));
-        for (int l = 0; l < nlayers; l++) {
-            e->append(seq, l, n, T, static_cast<const char *>(K) + l * kv_stride, static_cast<const char *>(V) + l * kv_stride);
-            e->attend(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, static_cast<char *>(O) + l * o_stride);
-        }
+        e->step_layers(seq, nlayers, n, T, K, V, Q, O, kv_stride, q_stride, o_stride);
         return 0;
     });
 }

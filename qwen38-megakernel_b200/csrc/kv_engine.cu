@@ -472,6 +472,31 @@ void KvEngine::append(int seq, int layer, int pos0, int n, const void * K, const
     s.kv_top = std::max(s.kv_top, pos0 + n);
 }
 
+void KvEngine::step_layers(int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O, size_t kv_stride,
+                           size_t q_stride, size_t o_stride) {
+    use_device();
+    if (nlayers < 0 || nlayers > cfg_.layers) throw std::runtime_error("step_layers: nlayers must be 0.." + std::to_string(cfg_.layers));
+    if (nlayers == 0) return;
+    Seq & s = seq_ref(seq);
+    // The appends of all layers are independent of one another and of the previous layers' attention: they go out as one launch
+    // (the per-layer form costs a launch between every two attention kernels). Anything the single-layer append would do first
+    // is done first here too; a step too long for one ring piece takes the per-layer route.
+    const bool one_launch = T >= 1 && T <= MAXT && K && V && n >= s.base && (long long) n + T - s.base <= s.ctx && kv_stride % 2 == 0;
+    if (one_launch) {
+        if (seq == SEQ_MAIN && sw_on_) sw_need(n + T);
+        wait_copies(s);
+        if (cfg_.spill && rc_ > 0)
+            for (int l = 0; l < nlayers; l++) spill_to(s, l, n + T - rc_); // rows about to be displaced get their main-format row first
+        MKKV_CK(launch_append_layers(s.d_views, nlayers, static_cast<const uint16_t *>(K), static_cast<const uint16_t *>(V), kv_stride, n, T, stream_));
+        launches_++;
+        s.kv_top = std::max(s.kv_top, n + T);
+    }
+    for (int l = 0; l < nlayers; l++) {
+        if (!one_launch) append(seq, l, n, T, static_cast<const char *>(K) + l * kv_stride, static_cast<const char *>(V) + l * kv_stride);
+        attend(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, static_cast<char *>(O) + l * o_stride);
+    }
+}
+
 void KvEngine::ensure_work(int items, int njobs) {
     if (items > work_items_) {
         MKKV_CK(cudaStreamSynchronize(stream_));

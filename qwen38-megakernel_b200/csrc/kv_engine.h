@@ -119,6 +119,9 @@ class KvEngine {
     void kv_sizes(size_t * per_token, size_t * rings, size_t * state, size_t * checkpoint) const;
     // The reference's prompt-state file (state_files.cu:97-238) of rows 0 .. hend - 1, the rings and the caller's extra regions
     // (device or host pointers). save: the file's size; load: true when the file exists and matches key, hend and every region size.
+    // one decode step over layers 0 .. nlayers - 1: one append launch for every layer's T rows at n, then the layers' attention
+    void step_layers(int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O, size_t kv_stride, size_t q_stride,
+                     size_t o_stride);
     void unpack_probe(int bits, const void * rows, const void * scales, int nrows, void * out); // (test probe of the unpack step)
     long long state_save(int seq, const char * path, const void * key, size_t key_len, int hend, const void * const * extra,
                          const size_t * extra_sizes, int n_extra);

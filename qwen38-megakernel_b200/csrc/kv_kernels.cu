@@ -111,6 +111,23 @@ __global__ void __launch_bounds__(256) append_batch_kernel(const AppendJob * job
     const int t = idx / (2 * NKV), w = (idx / NKV) & 1, g = idx % NKV, pos = j.pos0 + t;
     append_row(j.kv, w, g, pos, (w ? j.V : j.K) + ((size_t) t * NKV + g) * HD, lane);
 }
+// the same rows for every layer of one sequence in one launch: layer = blockIdx.y, its K / V rows kv_stride bytes after the previous
+// layer's (the views are the sequence's device-resident array, so a decode step uploads nothing)
+__global__ void __launch_bounds__(256) append_layers_kernel(const KvView * views, const uint16_t * K, const uint16_t * V, size_t kv_stride, int pos0,
+                                                            int n) {
+    const KvView & kv = views[blockIdx.y];
+    const int lane = threadIdx.x & 31, idx = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (idx >= n * 2 * NKV) return;
+    const int t = idx / (2 * NKV), w = (idx / NKV) & 1, g = idx % NKV;
+    const uint16_t * src = reinterpret_cast<const uint16_t *>(reinterpret_cast<const char *>(w ? V : K) + blockIdx.y * kv_stride);
+    append_row(kv, w, g, pos0 + t, src + ((size_t) t * NKV + g) * HD, lane);
+}
+cudaError_t launch_append_layers(const KvView * views_dev, int nlayers, const uint16_t * K, const uint16_t * V, size_t kv_stride, int pos0, int n,
+                                 cudaStream_t stream) {
+    if (nlayers <= 0 || n <= 0) return cudaSuccess;
+    append_layers_kernel<<<dim3((n * 2 * NKV + 7) / 8, nlayers), 256, 0, stream>>>(views_dev, K, V, kv_stride, pos0, n);
+    return cudaGetLastError();
+}
 cudaError_t launch_append_batch(const AppendJob * jobs_dev, int njobs, int max_n, cudaStream_t stream) {
     if (njobs <= 0 || max_n <= 0) return cudaSuccess;
     append_batch_kernel<<<dim3((max_n * 2 * NKV + 7) / 8, njobs), 256, 0, stream>>>(jobs_dev);
@@ -237,7 +254,7 @@ static float * g_static_part_addr[64] = {};
 static float2 * g_static_ml_addr[64] = {};
 cudaError_t preload_kernels() {
     cudaFuncAttributes fa;
-    const void * fns[] = {(const void *) append_kernel, (const void *) spill_kernel, (const void *) refill_kernel, (const void *) append_batch_kernel,
+    const void * fns[] = {(const void *) append_kernel, (const void *) spill_kernel, (const void *) refill_kernel, (const void *) append_batch_kernel, (const void *) append_layers_kernel,
                           (const void *) gather_kernel, (const void *) attn_merge_kernel};
     for (const void * f : fns) {
         const cudaError_t e = cudaFuncGetAttributes(&fa, f);

@@ -77,6 +77,9 @@ struct AppendJob {
     int pos0, n;
 };
 cudaError_t launch_append_batch(const AppendJob * jobs_dev, int njobs, int max_n, cudaStream_t stream);
+// rows pos0 .. pos0 + n - 1 of layers 0 .. nlayers - 1 of one sequence in one launch (views_dev: the sequence's device array of views)
+cudaError_t launch_append_layers(const KvView * views_dev, int nlayers, const uint16_t * K, const uint16_t * V, size_t kv_stride, int pos0, int n,
+                                 cudaStream_t stream);
 
 // Snapshot gather / restore scatter between the cache regions of one sequence and a contiguous staging buffer.
 // The snapshot byte stream is, region after region, rows [a, b) of every main region and ring rows [ra, rb) of every ring
