@@ -698,10 +698,23 @@ void KvEngine::step_layers_partial(int seq, int nlayers, int n, int T, const voi
     if (nlayers < 0 || nlayers > cfg_.layers) throw std::runtime_error("step_layers_partial: nlayers must be 0.." + std::to_string(cfg_.layers));
     if (T < 1 || T > MAXT) throw std::runtime_error("step_layers_partial: T must be 1.." + std::to_string(MAXT));
     const int a = std::max(n, own_lo), b = std::min(n + T, own_hi), hi = std::min(pos_hi, n + T);
+    if (b > a && nlayers > 0) { // the rows this rank owns, every layer in one launch (as step_layers)
+        use_device();
+        Seq & s = seq_ref(seq);
+        if (!K || !V) throw std::runtime_error("step_layers_partial: null K / V");
+        if (a < s.base || (long long) b - s.base > s.ctx)
+            throw std::runtime_error("step_layers_partial: rows " + std::to_string(a) + " .. " + std::to_string(b) + " outside the sequence's rows");
+        if (seq == SEQ_MAIN && sw_on_) sw_need(b);
+        wait_copies(s);
+        if (cfg_.spill && rc_ > 0)
+            for (int l = 0; l < nlayers; l++) spill_to(s, l, b - rc_);
+        const size_t skip = (size_t) (a - n) * NKV * HD * 2;
+        MKKV_CK(launch_append_layers(s.d_views, nlayers, reinterpret_cast<const uint16_t *>(static_cast<const char *>(K) + skip),
+                                     reinterpret_cast<const uint16_t *>(static_cast<const char *>(V) + skip), kv_stride, a, b - a, stream_));
+        launches_++;
+        s.kv_top = std::max(s.kv_top, b);
+    }
     for (int l = 0; l < nlayers; l++) {
-        if (b > a)
-            append(seq, l, a, b - a, static_cast<const char *>(K) + l * kv_stride + (size_t) (a - n) * NKV * HD * 2,
-                   static_cast<const char *>(V) + l * kv_stride + (size_t) (a - n) * NKV * HD * 2);
         attend_partial(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, pos_lo, hi > pos_lo ? hi : pos_lo,
                        static_cast<float *>(parts) + (size_t) l * NKV * AR * HD, static_cast<float *>(mls) + (size_t) l * NKV * AR * 2);
     }
