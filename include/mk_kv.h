@@ -105,7 +105,8 @@ int mk_kv_combine_layers_strided(void * h, int nlayers, int T, int nparts, const
 int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O);
 /* One decode step over layers 0 .. nlayers - 1 in one call: layer l appends T rows at n from K + l kv_stride, V + l kv_stride
  * and attends with Q + l q_stride into O + l o_stride (strides in bytes). What the reference's forward pass does between its
- * layers' attention phases (engine.cu:1353-1413) with the host out of the loop; equal to nlayers calls of mk_kv_step. */
+ * layers' attention phases (engine.cu:1353-1413) with the host out of the loop; equal in result to nlayers calls of mk_kv_step (the
+ * rows of all layers are appended by one launch before the first layer's attention: every K and V must be complete at the call). */
 int mk_kv_step_layers(void * h, int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O,
                       size_t kv_stride, size_t q_stride, size_t o_stride);
 /* lanes_step (lanes.cu:452-560): one pass over several sequences; job j runs T[j] tokens at n[j] of sequence seqs[j].
