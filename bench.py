@@ -576,17 +576,16 @@ def main():
             eng.step_layers(n, Kd[:, :T], Vd[:, :T], Qd[:, :T], Od[:, :T])
         advance(n, T)
 
-    filler = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")
 
     def timed_attends(pairs):
-        """a step whose attention launches (one per layer, back to back, nothing between them) sit inside one event pair; a few ms of
-        device work is queued first so that the host is ahead of the device and the pair times device work only"""
+        """a step whose attention launches (one per layer, back to back, nothing between them) sit inside one event pair; about 2 ms
+        of device time (a spin, no memory traffic) is queued first so that the host is ahead of the device and the pair times device
+        work only"""
         n = state["n"]
         T = mk.cap_T(n, T_STEP)
         for l in range(layers):
             eng.append_raw(l, n, T, Kd[l], Vd[l])
-        for _ in range(6):
-            filler.fill_(1)
+        torch.cuda._sleep(4_000_000)  # about 2 ms of device time without memory traffic: the launches below queue up behind it
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for l in range(layers):
@@ -646,7 +645,6 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         att_us = float(t.item())
     eng.close()
-    del filler
     torch.cuda.empty_cache()
 
     line = None
