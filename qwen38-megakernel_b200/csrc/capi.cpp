@@ -199,8 +199,7 @@ int mk_kv_attend_static(void * hp, int seq, int layer, int n, int T, const void 
 }
 int mk_kv_step(void * hp, int seq, int layer, int n, int T, const void * K, const void * V, const void * Q, void * O) {
     return guarded(hp, [&](KvEngine * e) {
-        e->append(seq, layer, n, T, K, V);
-        e->attend(seq, layer, n, T, Q, O);
+        e->step_layers(seq, 1, n, T, K, V, Q, O, 0, 0, 0, layer); // (one append launch that also stages the queries, then the attention)
         return 0;
     });
 }

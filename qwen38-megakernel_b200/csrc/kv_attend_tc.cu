@@ -11,6 +11,8 @@
 //     AND-OR each, kv_unpack.h, which leaves the 8 dims of a 16-byte unit in the order UNIT_PERM: the queries are staged in the
 //     same order and the output dims are mapped back) -- K as the K-major A operand of S^T[128 pos x 48 rows] = K Q^T, V as the
 //     MN-major A operand of O^T[256 dims x 48 rows] += V^T P^T;
+//   - the queries arrive staged (qprep in kv_kernels.cu: rotated when K is, x 1/16, fp16, in the B operand's layout; made once per
+//     (job, kv head) by the decode step's append launch or a small launch of its own) and are fetched with one bulk copy;
 //   - one issuer thread runs tcgen05.mma on the slots as they fill (mbarrier "full" from the unpack warps, tcgen05.commit
 //     to "empty"), S^T in five tensor-memory buffers (K runs five groups ahead of V), O^T (two 128-dim halves) resident there
 //     for the whole kernel;
@@ -78,6 +80,7 @@ constexpr int NTASK = 16;
 constexpr int Q_BYTES = AR * HD * 2, P_BYTES = AR * GP * 2;
 constexpr unsigned S_COL = 0, S_STRIDE = 64, O_COL0 = NSB * 64, O_COL1 = O_COL0 + 2 * AR, TMEM_COLS = 512; // an O^T half: 48 columns for P's high part, 48 for its low part
 static_assert(O_COL1 + 2 * AR <= TMEM_COLS, "tensor-memory columns");
+static_assert(Q_BYTES == QP_HEAD_BYTES, "the staged query block of a kv head");
 // The accumulator's reference max of a row is set REF_MARGIN above the running max it is taken from and moves when the running max
 // passes it by more than REF_SLACK: exp(running - reference) stays within [e^-3 for the row's largest terms, e^10.5 < fp16 max].
 constexpr float REF_SLACK = 10.5f, REF_MARGIN = 3.f;
@@ -331,7 +334,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         mbar_init(&sm.p_full, NSOFT);
         mbar_init(&sm.p_empty, 1);
         mbar_init(&sm.fin, 1);
-        mbar_init(&sm.q_ready, NTHREADS / 32 - 1);
+        mbar_init(&sm.q_ready, 1);
         sm.wc.dead = 0;
         sm.wc.hint = a.wait_hint_ns;
         sm.wc.rounds = a.wait_rounds;
@@ -364,53 +367,18 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
     auto get_task = [&](int t) -> Task { return batch ? make_task(geo4.g, GT, 1, t, c_fixed) : ttab ? ttab[t] : make_task4(geo4, t); };
     const int G = kk < t_end ? (t_end - kk + tstep - 1) / tstep : 0; // this CTA's groups: tasks kk, kk + tstep, ..
 
-    // query rows of the kv head: fp16 -> fp32 -> (K's rotation) -> x 1/16 -> fp16 (qwen38_mk.cu:2876-2883), row = (head % 6) T + t,
-    // as the K-major B operand: lane holds dims 8 lane .. + 7 = one 16-byte unit. Every warp but the producer stages its share at
-    // once (the producer goes straight to its copies, so the first packed tiles are on their way meanwhile); the issuer waits for
-    // all of them.
-    auto stage_q = [&]() {
-        constexpr int NQW = NTHREADS / 32 - 1;
-        const int qw = warp < W_PROD ? warp : warp - 1;
-        uint4 rawq[(AR + NQW - 1) / NQW];
-#pragma unroll
-        for (int i = 0; i < (AR + NQW - 1) / NQW; i++) { // (all of the warp's rows are requested before the first is used)
-            const int r = qw + i * NQW;
-            rawq[i] = make_uint4(0, 0, 0, 0);
-            if (r < R) rawq[i] = *reinterpret_cast<const uint4 *>(J.Q + ((size_t) (r % T) * NH + g * GQ + r / T) * HD + lane * 8);
-        }
-#pragma unroll
-        for (int i = 0; i < (AR + NQW - 1) / NQW; i++) {
-            const int r = qw + i * NQW;
-            if (r >= AR) break;
-            uint4 out = make_uint4(0, 0, 0, 0);
-            if (r < R) {
-                const __half2 * hh = reinterpret_cast<const __half2 *>(&rawq[i]);
-                float v[8];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const float2 f = __half22float2(hh[k]);
-                    v[2 * k] = f.x;
-                    v[2 * k + 1] = f.y;
-                }
-                if (kv.s[0].rot) fwht256(v, lane);
-                __half2 * h = reinterpret_cast<__half2 *>(&out);
-#pragma unroll
-                for (int k = 0; k < 4; k++) // the unit's dims in the order the unpack warps leave K's (unit_perm)
-                    h[k] = __floats2half2_rn(__fmul_rn(v[unit_perm(2 * k)], 0.0625f), __fmul_rn(v[unit_perm(2 * k + 1)], 0.0625f));
-            }
-            *reinterpret_cast<uint4 *>(sm.q + lane * (AR / 8 * 128) + (r >> 3) * 128 + (r & 7) * 16) = out;
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.q_ready);
-    };
-    if (warp != W_PROD) stage_q(); // (one copy of that code, before the roles part; the producer is already fetching)
+    // The kv head's query rows come staged (qprep: fp16 -> fp32 -> K's rotation -> x 1/16 -> fp16 in the K-major B operand's layout,
+    // row = (head % 6) T + t): the producer fetches the block with one bulk copy, the issuer waits for it.
     // registers move from the unpack / control warps to the softmax warps
     if (warp >= W_ISSUE) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 " MKKV_TC_REGS_CTL ";");
     if (warp == W_PROD) {
         // ---- producer: K(0) .. K(NSB - 1), then V(i), K(i + NSB) -- the order the unpack warps consume. Lanes 0 .. 3 fetch one
         // tile of the group each ----
+        if (lane == 0) { // the queries first
+            mbar_expect_tx(&sm.q_ready, Q_BYTES);
+            bulk_g2s(sm.q, reinterpret_cast<const uint8_t *>(J.Qp) + (size_t) g * Q_BYTES, Q_BYTES, &sm.q_ready);
+        }
         if (lane < GT) {
             const SideSrc ksrc = make_src(kv, 0, g, ws), vsrc = make_src(kv, 1, g, ws);
             unsigned rseq = lane; // this lane's tile in the sequence of all tiles of all side-groups
@@ -443,6 +411,8 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
             }
             // a CTA whose waits gave up reaches this point with copies possibly in flight: they must land before the CTA's shared
             // memory is released (bounded; in a normal run every copy was waited for by its consumer long ago)
+            if (sm.wc.dead && lane == 0) // (the query block too)
+                for (unsigned it = 0; it < (1u << 14) && !mbar_try_wait_hint(&sm.q_ready, 0u, 1000u); it++) {}
             if (sm.wc.dead)
                 for (int j = 0; j < 3; j++) {
                     const unsigned e = (issued >> (8 * j)) & 0xffu;
@@ -1043,6 +1013,7 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
                              unsigned long long * xb, int nbmax, int epoch, int * status, cudaStream_t stream, const AttnTask * tasks_dev,
                              int ntasks, int tasks_B, float * raw_part, float2 * raw_ml, unsigned long long * prof, unsigned * done,
                              unsigned * done_seq) {
+    if (!job.Qp) return cudaErrorNotSupported; // (the queries were not staged: the caller takes its other kernel)
     tc::Args a;
     a.prof = prof;
     a.one = job;
@@ -1096,6 +1067,8 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
 cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
                                    float2 * ml, int part_slots, int * status, cudaStream_t stream) {
     if (njobs < 1 || total_items < 1 || total_items > part_slots || !jobs_dev) return cudaErrorNotSupported;
+    for (int j = 0; j < njobs; j++)
+        if (!jobs_host[j].Qp) return cudaErrorNotSupported; // (queries not staged)
     tc::Args a;
     a.one = jobs_host[0];
     a.jobs = jobs_dev;

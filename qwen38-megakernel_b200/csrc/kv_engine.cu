@@ -157,6 +157,7 @@ void KvEngine::init_device_state() {
         }
     alloc_seq(main_, cfg.ctx);
     ensure_work(std::max(NKV * ATT_NCH, num_sms_), 1);
+    ensure_qprep(cfg.layers);
 }
 
 // exchange arrays of the spread attention kernels: two of [4][20][nb][48] words (zeroed: no word carries a launch tag yet)
@@ -235,6 +236,7 @@ void KvEngine::release() {
     cudaFree(staging_);
     cudaFree(xmax_);
     cudaFree(tc_done_);
+    cudaFree(qprep_);
     cudaFree(prof_);
     if (h_status_) cudaFreeHost(h_status_);
     if (ev_compute_) cudaEventDestroy(ev_compute_);
@@ -473,28 +475,59 @@ void KvEngine::append(int seq, int layer, int pos0, int n, const void * K, const
 }
 
 void KvEngine::step_layers(int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O, size_t kv_stride,
-                           size_t q_stride, size_t o_stride) {
+                           size_t q_stride, size_t o_stride, int layer0) {
     use_device();
-    if (nlayers < 0 || nlayers > cfg_.layers) throw std::runtime_error("step_layers: nlayers must be 0.." + std::to_string(cfg_.layers));
+    if (nlayers < 0 || layer0 < 0 || layer0 + nlayers > cfg_.layers)
+        throw std::runtime_error("step_layers: layers must lie in 0.." + std::to_string(cfg_.layers));
     if (nlayers == 0) return;
     Seq & s = seq_ref(seq);
     // The appends of all layers are independent of one another and of the previous layers' attention: they go out as one launch
-    // (the per-layer form costs a launch between every two attention kernels). Anything the single-layer append would do first
-    // is done first here too; a step too long for one ring piece takes the per-layer route.
+    // (the per-layer form costs a launch between every two attention kernels), and the same launch stages the layers' queries
+    // for the tensor-core kernel. Anything the single-layer append would do first is done first here too; a call it would
+    // refuse takes the per-layer route and gets its message there.
     const bool one_launch = T >= 1 && T <= MAXT && K && V && n >= s.base && (long long) n + T - s.base <= s.ctx && kv_stride % 2 == 0;
     if (one_launch) {
         if (seq == SEQ_MAIN && sw_on_) sw_need(n + T);
         wait_copies(s);
         if (cfg_.spill && rc_ > 0)
-            for (int l = 0; l < nlayers; l++) spill_to(s, l, n + T - rc_); // rows about to be displaced get their main-format row first
-        MKKV_CK(launch_append_layers(s.d_views, nlayers, static_cast<const uint16_t *>(K), static_cast<const uint16_t *>(V), kv_stride, n, T, stream_));
+            for (int l = layer0; l < layer0 + nlayers; l++) spill_to(s, l, n + T - rc_); // rows about to be displaced get their main-format row first
+        const bool stage = use_tc_ && Q && q_stride % 16 == 0 && reinterpret_cast<uintptr_t>(Q) % 16 == 0;
+        MKKV_CK(launch_append_layers(s.d_views + layer0, nlayers, static_cast<const uint16_t *>(K), static_cast<const uint16_t *>(V), kv_stride, n, T, stream_,
+                                     stage ? static_cast<const uint16_t *>(Q) : nullptr, q_stride, qprep_ + (size_t) layer0 * NKV * (QP_HEAD_BYTES / 2), T));
         launches_++;
         s.kv_top = std::max(s.kv_top, n + T);
+        for (int l = 0; l < nlayers && stage; l++) { // (the layers' attention calls below find their queries staged)
+            qprep_src_[layer0 + l] = static_cast<const char *>(Q) + l * q_stride;
+            qprep_T_[layer0 + l] = T;
+        }
     }
     for (int l = 0; l < nlayers; l++) {
-        if (!one_launch) append(seq, l, n, T, static_cast<const char *>(K) + l * kv_stride, static_cast<const char *>(V) + l * kv_stride);
-        attend(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, static_cast<char *>(O) + l * o_stride);
+        if (!one_launch) append(seq, layer0 + l, n, T, static_cast<const char *>(K) + l * kv_stride, static_cast<const char *>(V) + l * kv_stride);
+        attend(seq, layer0 + l, n, T, static_cast<const char *>(Q) + l * q_stride, static_cast<char *>(O) + l * o_stride);
     }
+}
+
+void KvEngine::ensure_qprep(int slots) {
+    if (slots <= qprep_slots_) return;
+    MKKV_CK(cudaStreamSynchronize(stream_));
+    cudaFree(qprep_);
+    qprep_ = nullptr;
+    MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&qprep_), (size_t) slots * NKV * QP_HEAD_BYTES));
+    qprep_slots_ = slots;
+    for (int l = 0; l < MAX_LAYERS; l++) qprep_src_[l] = nullptr;
+}
+// the job's queries in the tensor-core kernel's operand layout: slot `slot` of the staging buffer, filled here by a launch of its own
+// unless the decode step's append launch has just staged the very same rows
+const uint16_t * KvEngine::staged_q(AttnJob & j, int slot) {
+    j.Qp = qprep_ + (size_t) slot * NKV * (QP_HEAD_BYTES / 2);
+    if (slot < MAX_LAYERS && qprep_src_[slot] == j.Q && qprep_T_[slot] == j.T) {
+        qprep_src_[slot] = nullptr;
+        return j.Qp;
+    }
+    if (slot < MAX_LAYERS) qprep_src_[slot] = nullptr;
+    MKKV_CK(launch_qprep(nullptr, &j, 1, stream_));
+    launches_++;
+    return j.Qp;
 }
 
 void KvEngine::ensure_work(int items, int njobs) {
@@ -529,6 +562,7 @@ void KvEngine::reserve_batch(int njobs) {
     use_device();
     if (njobs < 1 || njobs > 4096) throw std::runtime_error("reserve_batch: njobs out of range");
     ensure_work(std::max(njobs * NKV * ATT_NCH, num_sms_), njobs);
+    ensure_qprep(std::max(njobs, cfg_.layers));
 }
 
 // a call that needs the whole sequence on this GPU: not for a sequence whose rows start at a non-zero base (mk_kv_set_base)
@@ -553,6 +587,7 @@ AttnJob KvEngine::whole_job(const Seq & s, const char * what, int layer, int n, 
     AttnJob j;
     j.kv = s.views[layer];
     j.Q = static_cast<const uint16_t *>(Q);
+    j.Qp = nullptr;
     j.O = static_cast<float *>(O);
     j.n = n;
     j.T = T;
@@ -575,9 +610,10 @@ void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O
     use_device();
     check_layer(layer);
     Seq & s = seq_ref(seq);
-    const AttnJob j = whole_job(s, "attend", layer, n, T, Q, O);
+    AttnJob j = whole_job(s, "attend", layer, n, T, Q, O);
     wait_copies(s);
     spill_to(s, layer, j.ws); // positions that left the window are read in the main format from now on
+    if (use_tc_) staged_q(j, layer);
     launch_attention(&j, 1, NKV * j.nch, T);
 }
 
@@ -610,6 +646,7 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
     AttnJob j;
     j.kv = s.views[layer];
     j.Q = static_cast<const uint16_t *>(Q);
+    j.Qp = nullptr;
     j.O = nullptr;
     j.n = n;
     j.T = T;
@@ -621,6 +658,7 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
     j.pstride = 1;
     j.rstride = 0;
     if (pos_hi > pos_lo) spill_to(s, layer, std::min(j.ws, pos_hi)); // rows of this range that left the window
+    if (use_tc_) staged_q(j, layer);
     std::vector<AttnTask> tasks;
     bool tc = use_tc_;
     for (;; tc = false) { // the tensor-core kernel first (4 tiles per task), else the fast kernel (8)
@@ -674,6 +712,7 @@ void KvEngine::combine(int layer, int T, int nparts, const void * parts, const v
     AttnJob j;
     j.kv = main_.views[layer]; // (only the V rotation flag is read)
     j.Q = nullptr;
+    j.Qp = nullptr;
     j.O = static_cast<float *>(O);
     j.n = 0;
     j.T = T;
@@ -698,21 +737,32 @@ void KvEngine::step_layers_partial(int seq, int nlayers, int n, int T, const voi
     if (nlayers < 0 || nlayers > cfg_.layers) throw std::runtime_error("step_layers_partial: nlayers must be 0.." + std::to_string(cfg_.layers));
     if (T < 1 || T > MAXT) throw std::runtime_error("step_layers_partial: T must be 1.." + std::to_string(MAXT));
     const int a = std::max(n, own_lo), b = std::min(n + T, own_hi), hi = std::min(pos_hi, n + T);
-    if (b > a && nlayers > 0) { // the rows this rank owns, every layer in one launch (as step_layers)
+    if (nlayers > 0) { // the rows this rank owns, every layer in one launch (as step_layers), with the layers' queries staged
         use_device();
         Seq & s = seq_ref(seq);
-        if (!K || !V) throw std::runtime_error("step_layers_partial: null K / V");
-        if (a < s.base || (long long) b - s.base > s.ctx)
-            throw std::runtime_error("step_layers_partial: rows " + std::to_string(a) + " .. " + std::to_string(b) + " outside the sequence's rows");
-        if (seq == SEQ_MAIN && sw_on_) sw_need(b);
-        wait_copies(s);
-        if (cfg_.spill && rc_ > 0)
-            for (int l = 0; l < nlayers; l++) spill_to(s, l, b - rc_);
-        const size_t skip = (size_t) (a - n) * NKV * HD * 2;
-        MKKV_CK(launch_append_layers(s.d_views, nlayers, reinterpret_cast<const uint16_t *>(static_cast<const char *>(K) + skip),
-                                     reinterpret_cast<const uint16_t *>(static_cast<const char *>(V) + skip), kv_stride, a, b - a, stream_));
-        launches_++;
-        s.kv_top = std::max(s.kv_top, b);
+        const int m = std::max(0, b - a);
+        if (m > 0) {
+            if (!K || !V) throw std::runtime_error("step_layers_partial: null K / V");
+            if (a < s.base || (long long) b - s.base > s.ctx)
+                throw std::runtime_error("step_layers_partial: rows " + std::to_string(a) + " .. " + std::to_string(b) + " outside the sequence's rows");
+            if (seq == SEQ_MAIN && sw_on_) sw_need(b);
+            wait_copies(s);
+            if (cfg_.spill && rc_ > 0)
+                for (int l = 0; l < nlayers; l++) spill_to(s, l, b - rc_);
+        }
+        const bool stage = use_tc_ && Q && q_stride % 16 == 0 && reinterpret_cast<uintptr_t>(Q) % 16 == 0;
+        if (m > 0 || stage) {
+            const size_t skip = (size_t) (m > 0 ? a - n : 0) * NKV * HD * 2;
+            MKKV_CK(launch_append_layers(s.d_views, nlayers, reinterpret_cast<const uint16_t *>(static_cast<const char *>(K) + skip),
+                                         reinterpret_cast<const uint16_t *>(static_cast<const char *>(V) + skip), kv_stride, a, m, stream_,
+                                         stage ? static_cast<const uint16_t *>(Q) : nullptr, q_stride, qprep_, T));
+            launches_++;
+        }
+        if (m > 0) s.kv_top = std::max(s.kv_top, b);
+        for (int l = 0; l < nlayers && stage; l++) {
+            qprep_src_[l] = static_cast<const char *>(Q) + l * q_stride;
+            qprep_T_[l] = T;
+        }
     }
     for (int l = 0; l < nlayers; l++) {
         attend_partial(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, pos_lo, hi > pos_lo ? hi : pos_lo,
@@ -734,6 +784,7 @@ void KvEngine::combine_layers(int nlayers, int T, int nparts, const void * parts
         AttnJob & j = h_jobs_[l];
         j.kv = main_.views[l]; // (only the V rotation flag is read)
         j.Q = nullptr;
+        j.Qp = nullptr;
         j.O = reinterpret_cast<float *>(static_cast<char *>(O) + l * o_stride);
         j.n = 0;
         j.T = T;
@@ -792,6 +843,7 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
         AttnJob & a = h_jobs_[j];
         a = whole_job(s, "step_batch", layer, n[j], T[j], static_cast<const uint16_t *>(Q) + row * NH * HD, static_cast<float *>(O) + row * NH * HD);
         a.item0 = items;
+        if (use_tc_ && j < qprep_slots_) a.Qp = qprep_ + (size_t) j * NKV * (QP_HEAD_BYTES / 2); // (staged below, every job in one launch)
         items += NKV * a.nch;
         maxT = std::max(maxT, T[j]);
         aj[j].kv = a.kv;
@@ -810,6 +862,11 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
     }
     MKKV_CK(cudaMemcpyAsync(d_jobs_, h_jobs_, sizeof(AttnJob) * njobs, cudaMemcpyHostToDevice, stream_));
     MKKV_CK(cudaEventRecord(ev_compute_, stream_));
+    if (use_tc_ && h_jobs_[0].Qp) {
+        for (int l = 0; l < MAX_LAYERS; l++) qprep_src_[l] = nullptr; // (the slots are the jobs' now)
+        MKKV_CK(launch_qprep(d_jobs_, h_jobs_, njobs, stream_));
+        launches_++;
+    }
     launch_attention(h_jobs_, njobs, items, maxT);
 }
 

@@ -121,7 +121,7 @@ class KvEngine {
     // (device or host pointers). save: the file's size; load: true when the file exists and matches key, hend and every region size.
     // one decode step over layers 0 .. nlayers - 1: one append launch for every layer's T rows at n, then the layers' attention
     void step_layers(int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O, size_t kv_stride, size_t q_stride,
-                     size_t o_stride);
+                     size_t o_stride, int layer0 = 0);
     void unpack_probe(int bits, const void * rows, const void * scales, int nrows, void * out); // (test probe of the unpack step)
     long long state_save(int seq, const char * path, const void * key, size_t key_len, int hend, const void * const * extra,
                          const size_t * extra_sizes, int n_extra);
@@ -192,6 +192,8 @@ class KvEngine {
     void need_whole(const Seq & s, const char * what) const;
     AttnJob whole_job(const Seq & s, const char * what, int layer, int n, int T, const void * Q, void * O) const;
     void unpark_into(Seq & s, int seq, int id);
+    void ensure_qprep(int slots);
+    const uint16_t * staged_q(AttnJob & j, int slot); // j.Qp = the slot; launches the staging unless the step's append launch did it
     std::vector<std::pair<char *, size_t>> state_regions(Seq & s, int hend) const;
     void spill_to(Seq & s, int layer, int upto);
     void ring_rewind(Seq & s, int P);
@@ -243,6 +245,10 @@ class KvEngine {
     int epoch_ = 0, num_sms_ = 0;
     bool use_tc_ = true;
     int xnb_ = 0; // batches per chunk the exchange arrays hold
+    uint16_t * qprep_ = nullptr;   // staged queries of the tensor-core kernel: [slot][4][QP_HEAD_BYTES]; slot = layer, or the job of a batch
+    int qprep_slots_ = 0;
+    const void * qprep_src_[MAX_LAYERS] = {}; // the Q pointer a layer's slot was staged from by the step's append launch (one use)
+    int qprep_T_[MAX_LAYERS] = {};
     unsigned * tc_done_ = nullptr; // fused merge of the tensor-core kernel: per kv head, CTAs done over all launches
     unsigned tc_done_seq_ = 0;     // launches that counted on it
     void ensure_xch(int nb);

@@ -73,6 +73,8 @@ struct KvView {
 struct AttnJob {
     KvView kv;
     const uint16_t * Q; // fp16 [T][24][256], post-norm / post-RoPE, unscaled
+    const uint16_t * Qp; // the same queries staged for the tensor-core kernel by qprep (kv_kernels.h): per kv head the 48 rows
+                         // (head % 6) T + t, rotated when K is, x 1/16, fp16, in the operand layout; null: not staged
     float * O;          // fp32 [T][24][256]
     int n, T;
     int nch, cs, ws;    // partition and window start of L = n + T

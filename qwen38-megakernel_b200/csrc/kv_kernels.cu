@@ -13,6 +13,7 @@
 #include "kv_kernels.h"
 #include "kv_quant.cuh"
 #include "kv_merge.cuh"
+#include "kv_unpack.h"
 
 namespace mkkv {
 
@@ -111,21 +112,83 @@ __global__ void __launch_bounds__(256) append_batch_kernel(const AppendJob * job
     const int t = idx / (2 * NKV), w = (idx / NKV) & 1, g = idx % NKV, pos = j.pos0 + t;
     append_row(j.kv, w, g, pos, (w ? j.V : j.K) + ((size_t) t * NKV + g) * HD, lane);
 }
-// the same rows for every layer of one sequence in one launch: layer = blockIdx.y, its K / V rows kv_stride bytes after the previous
-// layer's (the views are the sequence's device-resident array, so a decode step uploads nothing)
-__global__ void __launch_bounds__(256) append_layers_kernel(const KvView * views, const uint16_t * K, const uint16_t * V, size_t kv_stride, int pos0,
-                                                            int n) {
-    const KvView & kv = views[blockIdx.y];
+struct AttnArgs {
+    AttnJob one;          // the job when jobs == null
+    const AttnJob * jobs; // device array of njobs jobs
+    int njobs;
+    float * part;   // [items][AR][HD]
+    float2 * ml;    // [items][AR]
+};
+
+// One staged query row: row r (0 .. 47) of kv head g = query head g 6 + r / T, token r % T. lane: dims 8 lane .. + 7 = one 16-byte
+// unit of the operand layout.
+__device__ __forceinline__ void qprep_row(const uint16_t * Q, uint16_t * qp, int T, int rot, int g, int r, int lane) {
+    uint4 out = make_uint4(0, 0, 0, 0);
+    if (r < GQ * T) {
+        const uint4 rawq = *reinterpret_cast<const uint4 *>(Q + ((size_t) (r % T) * NH + g * GQ + r / T) * HD + lane * 8);
+        const __half2 * hh = reinterpret_cast<const __half2 *>(&rawq);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __half22float2(hh[k]);
+            v[2 * k] = f.x;
+            v[2 * k + 1] = f.y;
+        }
+        if (rot) fwht256(v, lane);
+        __half2 * h = reinterpret_cast<__half2 *>(&out);
+#pragma unroll
+        for (int k = 0; k < 4; k++) // the unit's dims in the order the unpack warps leave K's (unit_perm)
+            h[k] = __floats2half2_rn(__fmul_rn(v[unit_perm(2 * k)], 0.0625f), __fmul_rn(v[unit_perm(2 * k + 1)], 0.0625f));
+    }
+    uint8_t * dst = reinterpret_cast<uint8_t *>(qp) + (size_t) g * QP_HEAD_BYTES + lane * (AR / 8 * 128) + (r >> 3) * 128 + (r & 7) * 16;
+    *reinterpret_cast<uint4 *>(dst) = out;
+}
+constexpr int QP_BLOCKS = NKV * AR / 8; // blocks of 8 warps that stage one job's queries
+__global__ void __launch_bounds__(256) qprep_kernel(const __grid_constant__ AttnArgs a) {
+    const AttnJob & J = a.jobs ? a.jobs[blockIdx.y] : a.one;
     const int lane = threadIdx.x & 31, idx = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (!J.Qp) return;
+    qprep_row(J.Q, const_cast<uint16_t *>(J.Qp), J.T, J.kv.s[0].rot, idx / AR, idx % AR, lane);
+}
+cudaError_t launch_qprep(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, cudaStream_t stream) {
+    if (njobs <= 0) return cudaSuccess;
+    AttnArgs a;
+    a.one = jobs_host[0];
+    a.jobs = njobs > 1 ? jobs_dev : nullptr;
+    a.njobs = njobs;
+    a.part = nullptr;
+    a.ml = nullptr;
+    qprep_kernel<<<dim3(QP_BLOCKS, njobs), 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+// the same rows for every layer of one sequence in one launch: layer = blockIdx.y, its K / V rows kv_stride bytes after the previous
+// layer's (the views are the sequence's device-resident array, so a decode step uploads nothing). Blocks beyond the rows' stage the
+// layer's queries for the attention launch that follows (Q != null).
+__global__ void __launch_bounds__(256) append_layers_kernel(const KvView * views, const uint16_t * K, const uint16_t * V, size_t kv_stride, int pos0,
+                                                            int n, const uint16_t * Q, size_t q_stride, uint16_t * qp, int T) {
+    const KvView & kv = views[blockIdx.y];
+    const int lane = threadIdx.x & 31, nab = (n * 2 * NKV + 7) / 8;
+    if ((int) blockIdx.x >= nab) {
+        const int idx = ((int) blockIdx.x - nab) * 8 + (threadIdx.x >> 5);
+        qprep_row(reinterpret_cast<const uint16_t *>(reinterpret_cast<const char *>(Q) + blockIdx.y * q_stride),
+                  reinterpret_cast<uint16_t *>(reinterpret_cast<char *>(qp) + (size_t) blockIdx.y * NKV * QP_HEAD_BYTES), T, kv.s[0].rot, idx / AR, idx % AR,
+                  lane);
+        return;
+    }
+    const int idx = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (idx >= n * 2 * NKV) return;
     const int t = idx / (2 * NKV), w = (idx / NKV) & 1, g = idx % NKV;
     const uint16_t * src = reinterpret_cast<const uint16_t *>(reinterpret_cast<const char *>(w ? V : K) + blockIdx.y * kv_stride);
     append_row(kv, w, g, pos0 + t, src + ((size_t) t * NKV + g) * HD, lane);
 }
 cudaError_t launch_append_layers(const KvView * views_dev, int nlayers, const uint16_t * K, const uint16_t * V, size_t kv_stride, int pos0, int n,
-                                 cudaStream_t stream) {
-    if (nlayers <= 0 || n <= 0) return cudaSuccess;
-    append_layers_kernel<<<dim3((n * 2 * NKV + 7) / 8, nlayers), 256, 0, stream>>>(views_dev, K, V, kv_stride, pos0, n);
+                                 cudaStream_t stream, const uint16_t * Q, size_t q_stride, uint16_t * qp, int T) {
+    const bool stage = Q && qp && T > 0;
+    if (nlayers <= 0 || (n <= 0 && !stage)) return cudaSuccess; // (n == 0 with queries: the staging alone)
+    if (n < 0) n = 0;
+    append_layers_kernel<<<dim3((n * 2 * NKV + 7) / 8 + (stage ? QP_BLOCKS : 0), nlayers), 256, 0, stream>>>(views_dev, K, V, kv_stride, pos0, n,
+                                                                                                        stage ? Q : nullptr, q_stride, qp, T);
     return cudaGetLastError();
 }
 cudaError_t launch_append_batch(const AppendJob * jobs_dev, int njobs, int max_n, cudaStream_t stream) {
@@ -200,13 +263,6 @@ cudaError_t launch_gather(const CopyRegion * regions, int nregions, int a, int b
 // --------------------------------------------------------------------------------------------------------------------
 // merge of the decode-attention partials
 // --------------------------------------------------------------------------------------------------------------------
-struct AttnArgs {
-    AttnJob one;          // the job when jobs == null
-    const AttnJob * jobs; // device array of njobs jobs
-    int njobs;
-    float * part;   // [items][AR][HD]
-    float2 * ml;    // [items][AR]
-};
 
 // merge of the chunk partials of one (query head, token), one warp per row (kv_merge.cuh)
 __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__ AttnArgs a, int rows_per_job, int raw, float * part_out,
@@ -254,7 +310,7 @@ static float * g_static_part_addr[64] = {};
 static float2 * g_static_ml_addr[64] = {};
 cudaError_t preload_kernels() {
     cudaFuncAttributes fa;
-    const void * fns[] = {(const void *) append_kernel, (const void *) spill_kernel, (const void *) refill_kernel, (const void *) append_batch_kernel, (const void *) append_layers_kernel,
+    const void * fns[] = {(const void *) append_kernel, (const void *) spill_kernel, (const void *) refill_kernel, (const void *) append_batch_kernel, (const void *) append_layers_kernel, (const void *) qprep_kernel,
                           (const void *) gather_kernel, (const void *) attn_merge_kernel};
     for (const void * f : fns) {
         const cudaError_t e = cudaFuncGetAttributes(&fa, f);

@@ -77,9 +77,16 @@ struct AppendJob {
     int pos0, n;
 };
 cudaError_t launch_append_batch(const AppendJob * jobs_dev, int njobs, int max_n, cudaStream_t stream);
-// rows pos0 .. pos0 + n - 1 of layers 0 .. nlayers - 1 of one sequence in one launch (views_dev: the sequence's device array of views)
+// Queries staged for the tensor-core attention kernel (qwen38_mk.cu:2876-2883: fp16 -> fp32 -> K's rotation -> x 1/16 -> fp16), once
+// per (job, kv head) instead of once per CTA: QP_HEAD_BYTES bytes per kv head in that kernel's B-operand layout
+// [dim group 32][row group 6][8 rows][8 dims in the unpacked units' order], rows beyond 6 T zero. One bulk copy brings a head's block
+// into shared memory.
+constexpr int QP_HEAD_BYTES = AR * HD * 2;
+cudaError_t launch_qprep(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, cudaStream_t stream);
+// rows pos0 .. pos0 + n - 1 of layers 0 .. nlayers - 1 of one sequence in one launch (views_dev: the sequence's device array of views);
+// Q != null: the same launch stages the T query tokens of every layer (Q + l q_stride bytes -> qp + l * 4 * QP_HEAD_BYTES bytes)
 cudaError_t launch_append_layers(const KvView * views_dev, int nlayers, const uint16_t * K, const uint16_t * V, size_t kv_stride, int pos0, int n,
-                                 cudaStream_t stream);
+                                 cudaStream_t stream, const uint16_t * Q = nullptr, size_t q_stride = 0, uint16_t * qp = nullptr, int T = 0);
 
 // Snapshot gather / restore scatter between the cache regions of one sequence and a contiguous staging buffer.
 // The snapshot byte stream is, region after region, rows [a, b) of every main region and ring rows [ra, rb) of every ring
