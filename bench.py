@@ -51,7 +51,7 @@ SPEC = "K*=5r,V*=6"
 NH, NKV, HD = 24, 4, 256
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at this workload's shapes, from an ncu capture of the
 # one-layer case of this benchmark (a launch of the 16-layer run processes the same one layer); NCU_TRAFFIC_FROM says which
-NCU_TRAFFIC_BYTES = 163.3e6
+NCU_TRAFFIC_BYTES = 164.2e6
 NCU_TRAFFIC_FROM = "ncu capture of `bench.py --layers 1 --steps 2 --warmup 3 --no-cpu`, kernel attn_tc_kernel<5, 6>, one launch"
 WORKLOAD = "config2: 16 attention layers, 101,600 positions, preset F layout K5r/V6 + q8_0 window 2048, 8 queries/step, streaming append+spill+attend"
 REPEATS = 5  # the timed K-step loop is run this many times; the line's value is the median run
