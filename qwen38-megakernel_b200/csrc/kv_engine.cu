@@ -486,6 +486,7 @@ void KvEngine::step_layers(int seq, int nlayers, int n, int T, const void * K, c
     // for the tensor-core kernel. Anything the single-layer append would do first is done first here too; a call it would
     // refuse takes the per-layer route and gets its message there.
     const bool one_launch = T >= 1 && T <= MAXT && K && V && n >= s.base && (long long) n + T - s.base <= s.ctx && kv_stride % 2 == 0;
+    bool staged = false; // the layers' queries are staged by the append launch
     if (one_launch) {
         if (seq == SEQ_MAIN && sw_on_) sw_need(n + T);
         wait_copies(s);
@@ -496,14 +497,11 @@ void KvEngine::step_layers(int seq, int nlayers, int n, int T, const void * K, c
                                      stage ? static_cast<const uint16_t *>(Q) : nullptr, q_stride, qprep_ + (size_t) layer0 * NKV * (QP_HEAD_BYTES / 2), T));
         launches_++;
         s.kv_top = std::max(s.kv_top, n + T);
-        for (int l = 0; l < nlayers && stage; l++) { // (the layers' attention calls below find their queries staged)
-            qprep_src_[layer0 + l] = static_cast<const char *>(Q) + l * q_stride;
-            qprep_T_[layer0 + l] = T;
-        }
+        staged = stage;
     }
     for (int l = 0; l < nlayers; l++) {
         if (!one_launch) append(seq, layer0 + l, n, T, static_cast<const char *>(K) + l * kv_stride, static_cast<const char *>(V) + l * kv_stride);
-        attend(seq, layer0 + l, n, T, static_cast<const char *>(Q) + l * q_stride, static_cast<char *>(O) + l * o_stride);
+        attend_impl(seq, layer0 + l, n, T, static_cast<const char *>(Q) + l * q_stride, static_cast<char *>(O) + l * o_stride, staged);
     }
 }
 
@@ -514,20 +512,14 @@ void KvEngine::ensure_qprep(int slots) {
     qprep_ = nullptr;
     MKKV_CK(cudaMalloc(reinterpret_cast<void **>(&qprep_), (size_t) slots * NKV * QP_HEAD_BYTES));
     qprep_slots_ = slots;
-    for (int l = 0; l < MAX_LAYERS; l++) qprep_src_[l] = nullptr;
 }
 // the job's queries in the tensor-core kernel's operand layout: slot `slot` of the staging buffer, filled here by a launch of its own
-// unless the decode step's append launch has just staged the very same rows
-const uint16_t * KvEngine::staged_q(AttnJob & j, int slot) {
+// unless the caller (a decode step whose append launch staged every layer's queries a moment ago) says it is
+void KvEngine::staged_q(AttnJob & j, int slot, bool staged) {
     j.Qp = qprep_ + (size_t) slot * NKV * (QP_HEAD_BYTES / 2);
-    if (slot < MAX_LAYERS && qprep_src_[slot] == j.Q && qprep_T_[slot] == j.T) {
-        qprep_src_[slot] = nullptr;
-        return j.Qp;
-    }
-    if (slot < MAX_LAYERS) qprep_src_[slot] = nullptr;
+    if (staged) return;
     MKKV_CK(launch_qprep(nullptr, &j, 1, stream_));
     launches_++;
-    return j.Qp;
 }
 
 void KvEngine::ensure_work(int items, int njobs) {
@@ -606,14 +598,15 @@ AttnJob KvEngine::whole_job(const Seq & s, const char * what, int layer, int n, 
     return j;
 }
 
-void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O) {
+void KvEngine::attend(int seq, int layer, int n, int T, const void * Q, void * O) { attend_impl(seq, layer, n, T, Q, O, false); }
+void KvEngine::attend_impl(int seq, int layer, int n, int T, const void * Q, void * O, bool q_staged) {
     use_device();
     check_layer(layer);
     Seq & s = seq_ref(seq);
     AttnJob j = whole_job(s, "attend", layer, n, T, Q, O);
     wait_copies(s);
     spill_to(s, layer, j.ws); // positions that left the window are read in the main format from now on
-    if (use_tc_) staged_q(j, layer);
+    if (use_tc_) staged_q(j, layer, q_staged);
     launch_attention(&j, 1, NKV * j.nch, T);
 }
 
@@ -631,6 +624,10 @@ void KvEngine::set_base(int seq, int base) {
 }
 
 void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out) {
+    attend_partial_impl(seq, layer, n, T, Q, pos_lo, pos_hi, part_out, ml_out, false);
+}
+void KvEngine::attend_partial_impl(int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out,
+                                   bool q_staged) {
     use_device();
     check_layer(layer);
     Seq & s = seq_ref(seq);
@@ -658,7 +655,7 @@ void KvEngine::attend_partial(int seq, int layer, int n, int T, const void * Q, 
     j.pstride = 1;
     j.rstride = 0;
     if (pos_hi > pos_lo) spill_to(s, layer, std::min(j.ws, pos_hi)); // rows of this range that left the window
-    if (use_tc_) staged_q(j, layer);
+    if (use_tc_) staged_q(j, layer, q_staged);
     std::vector<AttnTask> tasks;
     bool tc = use_tc_;
     for (;; tc = false) { // the tensor-core kernel first (4 tiles per task), else the fast kernel (8)
@@ -737,6 +734,7 @@ void KvEngine::step_layers_partial(int seq, int nlayers, int n, int T, const voi
     if (nlayers < 0 || nlayers > cfg_.layers) throw std::runtime_error("step_layers_partial: nlayers must be 0.." + std::to_string(cfg_.layers));
     if (T < 1 || T > MAXT) throw std::runtime_error("step_layers_partial: T must be 1.." + std::to_string(MAXT));
     const int a = std::max(n, own_lo), b = std::min(n + T, own_hi), hi = std::min(pos_hi, n + T);
+    bool staged = false;
     if (nlayers > 0) { // the rows this rank owns, every layer in one launch (as step_layers), with the layers' queries staged
         use_device();
         Seq & s = seq_ref(seq);
@@ -759,14 +757,11 @@ void KvEngine::step_layers_partial(int seq, int nlayers, int n, int T, const voi
             launches_++;
         }
         if (m > 0) s.kv_top = std::max(s.kv_top, b);
-        for (int l = 0; l < nlayers && stage; l++) {
-            qprep_src_[l] = static_cast<const char *>(Q) + l * q_stride;
-            qprep_T_[l] = T;
-        }
+        staged = stage;
     }
     for (int l = 0; l < nlayers; l++) {
-        attend_partial(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, pos_lo, hi > pos_lo ? hi : pos_lo,
-                       static_cast<float *>(parts) + (size_t) l * NKV * AR * HD, static_cast<float *>(mls) + (size_t) l * NKV * AR * 2);
+        attend_partial_impl(seq, l, n, T, static_cast<const char *>(Q) + l * q_stride, pos_lo, hi > pos_lo ? hi : pos_lo,
+                            static_cast<float *>(parts) + (size_t) l * NKV * AR * HD, static_cast<float *>(mls) + (size_t) l * NKV * AR * 2, staged);
     }
 }
 
@@ -863,7 +858,6 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
     MKKV_CK(cudaMemcpyAsync(d_jobs_, h_jobs_, sizeof(AttnJob) * njobs, cudaMemcpyHostToDevice, stream_));
     MKKV_CK(cudaEventRecord(ev_compute_, stream_));
     if (use_tc_ && h_jobs_[0].Qp) {
-        for (int l = 0; l < MAX_LAYERS; l++) qprep_src_[l] = nullptr; // (the slots are the jobs' now)
         MKKV_CK(launch_qprep(d_jobs_, h_jobs_, njobs, stream_));
         launches_++;
     }

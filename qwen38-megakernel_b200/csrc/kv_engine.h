@@ -193,7 +193,10 @@ class KvEngine {
     AttnJob whole_job(const Seq & s, const char * what, int layer, int n, int T, const void * Q, void * O) const;
     void unpark_into(Seq & s, int seq, int id);
     void ensure_qprep(int slots);
-    const uint16_t * staged_q(AttnJob & j, int slot); // j.Qp = the slot; launches the staging unless the step's append launch did it
+    void staged_q(AttnJob & j, int slot, bool staged); // j.Qp = the slot; staged false: filled by a launch of its own (true: the step's
+                                                       // append launch has just done it)
+    void attend_impl(int seq, int layer, int n, int T, const void * Q, void * O, bool q_staged);
+    void attend_partial_impl(int seq, int layer, int n, int T, const void * Q, int pos_lo, int pos_hi, void * part_out, void * ml_out, bool q_staged);
     std::vector<std::pair<char *, size_t>> state_regions(Seq & s, int hend) const;
     void spill_to(Seq & s, int layer, int upto);
     void ring_rewind(Seq & s, int P);
@@ -247,8 +250,6 @@ class KvEngine {
     int xnb_ = 0; // batches per chunk the exchange arrays hold
     uint16_t * qprep_ = nullptr;   // staged queries of the tensor-core kernel: [slot][4][QP_HEAD_BYTES]; slot = layer, or the job of a batch
     int qprep_slots_ = 0;
-    const void * qprep_src_[MAX_LAYERS] = {}; // the Q pointer a layer's slot was staged from by the step's append launch (one use)
-    int qprep_T_[MAX_LAYERS] = {};
     unsigned * tc_done_ = nullptr; // fused merge of the tensor-core kernel: per kv head, CTAs done over all launches
     unsigned tc_done_seq_ = 0;     // launches that counted on it
     void ensure_xch(int nb);
