@@ -567,7 +567,9 @@ def main():
         """one decode step: every layer appends T rows and attends (one library call for the whole step)"""
         n = state["n"]
         T = mk.cap_T(n, T_STEP)
-        if host:  # end to end: this step's rows come from pinned host memory, the result goes back
+        if host:  # end to end: this step's rows come from pinned host memory, the result goes back (one copy per tensor: cutting the
+            # step into blocks of layers whose copies overlap the other blocks' attention measured slower, 114.6 against 109.8 us per
+            # layer: a small copy and a cross-stream event cost about 10 us each)
             Ks.copy_(Kh, non_blocking=True); Vs.copy_(Vh, non_blocking=True); Qs.copy_(Qh, non_blocking=True)
             eng.step_layers(n, Ks[:, :T], Vs[:, :T], Qs[:, :T], Od[:, :T])
             Oh.copy_(Od, non_blocking=True)

@@ -109,6 +109,10 @@ int mk_kv_step(void * h, int seq, int layer, int n, int T, const void * K, const
  * rows of all layers are appended by one launch before the first layer's attention: every K and V must be complete at the call). */
 int mk_kv_step_layers(void * h, int seq, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O,
                       size_t kv_stride, size_t q_stride, size_t o_stride);
+/* The same for layers layer0 .. layer0 + nlayers - 1 (K, V, Q, O point at layer0's rows): a host that receives a step's rows in
+ * blocks of layers overlaps the next block's copies with this block's attention. */
+int mk_kv_step_layers_at(void * h, int seq, int layer0, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O,
+                         size_t kv_stride, size_t q_stride, size_t o_stride);
 /* lanes_step (lanes.cu:452-560): one pass over several sequences; job j runs T[j] tokens at n[j] of sequence seqs[j].
  * K, V [sum T][4][256], Q [sum T][24][256], O [sum T][24][256] packed in job order. seqs, n, T are host arrays.
  * mk_kv_reserve_batch(njobs) must have been called once with at least this many jobs. */

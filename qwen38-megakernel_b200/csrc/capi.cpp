@@ -210,6 +210,13 @@ int mk_kv_step_layers(void * hp, int seq, int nlayers, int n, int T, const void 
         return 0;
     });
 }
+int mk_kv_step_layers_at(void * hp, int seq, int layer0, int nlayers, int n, int T, const void * K, const void * V, const void * Q, void * O,
+                         size_t kv_stride, size_t q_stride, size_t o_stride) {
+    return guarded(hp, [&](KvEngine * e) {
+        e->step_layers(seq, nlayers, n, T, K, V, Q, O, kv_stride, q_stride, o_stride, layer0);
+        return 0;
+    });
+}
 int mk_kv_reserve_batch(void * hp, int njobs) {
     return guarded(hp, [&](KvEngine * e) {
         e->reserve_batch(njobs);

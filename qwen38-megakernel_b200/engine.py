@@ -57,6 +57,7 @@ def load_library():
         "mk_kv_combine_layers_strided": (i, [vp, i, i, i, vp, vp, C.c_size_t, vp, C.c_size_t]),
         "mk_kv_step": (i, [vp, i, i, i, i, vp, vp, vp, vp]),
         "mk_kv_step_layers": (i, [vp, i, i, i, i, vp, vp, vp, vp, C.c_size_t, C.c_size_t, C.c_size_t]),
+        "mk_kv_step_layers_at": (i, [vp, i, i, i, i, i, vp, vp, vp, vp, C.c_size_t, C.c_size_t, C.c_size_t]),
         "mk_kv_reserve_batch": (i, [vp, i]),
         "mk_kv_step_batch": (i, [vp, i, ip, i, ip, ip, vp, vp, vp, vp]),
         "mk_kv_attend_batch": (i, [vp, i, ip, i, ip, ip, vp, vp]),
@@ -252,6 +253,15 @@ class Engine:
         self._ck(self.L.mk_kv_step_layers(self.h, seq, K.shape[0], n, Q.shape[1], K.data_ptr(), V.data_ptr(), Q.data_ptr(), O.data_ptr(),
                                           K.stride(0) * K.element_size(), Q.stride(0) * Q.element_size(), O.stride(0) * O.element_size()),
                  "step_layers")
+
+    def step_layers_at(self, layer0, n, K, V, Q, O, seq=SEQ_MAIN):
+        """step_layers for layers layer0 .. layer0 + K.shape[0] - 1 (the tensors hold those layers only)"""
+        for x in (K, V, Q, O):
+            if not x.is_cuda or not x[0].is_contiguous():
+                raise EngineError("step_layers_at: expected CUDA tensors whose per-layer rows are contiguous")
+        self._ck(self.L.mk_kv_step_layers_at(self.h, seq, layer0, K.shape[0], n, Q.shape[1], K.data_ptr(), V.data_ptr(), Q.data_ptr(), O.data_ptr(),
+                                             K.stride(0) * K.element_size(), Q.stride(0) * Q.element_size(), O.stride(0) * O.element_size()),
+                 "step_layers_at")
 
     def reserve_batch(self, njobs):
         self._ck(self.L.mk_kv_reserve_batch(self.h, njobs), "reserve_batch")

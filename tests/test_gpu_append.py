@@ -179,7 +179,20 @@ def test_step_layers_equals_per_layer_steps(mk, torch_cuda):
             ra, sa = a.read_row(l, side, 2, L + T - 1)
             rb, sb = b.read_row(l, side, 2, L + T - 1)
             assert np.array_equal(ra, rb) and np.array_equal(sa, sb)
-    a.close(); b.close()
+    # the same steps in blocks of layers (mk_kv_step_layers_at): layers 0 .. 1, then layer 2
+    c = mk.Engine(NL, L + 64, spec, win)
+    for l in range(NL):
+        K, V = kvdata.kv_rows(7 + l, l, 0, L)
+        c.append(l, 0, torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
+    Oc = torch.zeros_like(Oa)
+    for n0, rows in ((L, slice(0, T)), (L + T, slice(0, 2))):
+        c.step_layers_at(0, n0, Ks[:2, rows], Vs[:2, rows], Qs[:2, rows], Oc[:2, rows])
+        c.step_layers_at(2, n0, Ks[2:, rows], Vs[2:, rows], Qs[2:, rows], Oc[2:, rows])
+    c.sync()
+    assert torch.equal(Oc, Oa)
+    with pytest.raises(mk.EngineError, match="layers must lie"):
+        c.step_layers_at(2, L + T + 2, Ks[:2, :1], Vs[:2, :1], Qs[:2, :1], Oc[:2, :1])
+    a.close(); b.close(); c.close()
 
 
 def test_per_layer_spec_items_match_oracle(mk, torch_cuda):
