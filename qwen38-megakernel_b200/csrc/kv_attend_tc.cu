@@ -1,11 +1,11 @@
 // Decode attention on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory) for one sequence spread over
-// every SM. Same arithmetic as the other two attention kernels (the reference's attn_core_t, qwen38_mk.cu:2756-3067): the
+// every SM. Same arithmetic as the other attention kernel (the reference's attn_core_t, qwen38_mk.cu:2756-3067): the
 // chunk partition attn_dims, 32-position tiles in order inside a chunk with a running max, P = fp16(exp(S - max)), fp32
 // accumulation. The structure is a warp-specialised dequantising GEMM main loop:
 //   - the unit of work is a group of 4 consecutive tiles (128 positions) of one chunk; the groups of a kv head are dealt in
 //     group-major order to the CTAs of that head (cooperative launch: all CTAs resident);
-//   - one producer thread streams the packed K / V rows of the CTA's groups into a ring of shared-memory slots with bulk
-//     copies completing on mbarriers;
+//   - four producer lanes (a tile each) stream the packed K / V rows of the CTA's groups into a ring of shared-memory slots with
+//     bulk copies completing on mbarriers;
 //   - 16 unpack warps turn packed rows into exact fp16(d * q) operands in the canonical no-swizzle UMMA layouts (one thread:
 //     one position x 32 dims per step; the fp16 pairs are assembled straight from the nibble words and high-bit fields with one
 //     AND-OR each, kv_unpack.h, which leaves the 8 dims of a 16-byte unit in the order UNIT_PERM: the queries are staged in the
@@ -19,12 +19,13 @@
 //   - 8 softmax warps read S^T back (tcgen05.ld: a thread owns one position and 24 query rows), take the tile maxima (two
 //     groups ahead of P, so that a group's own maxima are published long before another CTA needs them), exchange the running
 //     max with the CTAs that hold the chunk's earlier groups through small global arrays (own group maxima and cumulative
-//     maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as the B operand. The accumulator is kept against a per-row reference max that moves rarely (when the running max passes
-//     it by more than 10.5): P, after its fp16 rounding, is multiplied by exp(running max - reference) and carried as an fp16
+//     maxima, 8-byte {launch tag, value} words, polled with a bound), and write P to shared memory as the B operand. The
+//     accumulator is kept against a per-row reference max that moves rarely (when the running max passes it by more than 10.5;
+//     then the moved rows' accumulator columns are rescaled, one tensor-memory column per row and block): P, after its fp16 rounding, is multiplied by exp(running max - reference) and carried as an fp16
 //     high and low part (one N = 96 MMA per k-step, two 48-column accumulator blocks), so the reference's fp16 P is reproduced
 //     and no per-tile accumulator rescale is needed;
 //   - a CTA writes one un-normalised partial (m, l, O); when the CTAs of a kv head have all written theirs (arrival count,
-//     bounded wait) each merges one or two of the head's rows in the kernel's tail (merge_row);
+//     bounded wait) each merges one or two of the head's rows in the kernel's tail, four warps to a row;
 //   - batch mode (several jobs): one CTA per (job, kv head, chunk) in a plain launch, the chunk's groups in order on that CTA with
 //     the running max carried in registers; attn_merge_kernel afterwards.
 // Every wait is bounded (about two seconds by default; the limits are launch arguments), then the status word and a CTA-wide
