@@ -73,7 +73,8 @@ static_assert(NTHREADS == 640 && 8 * 128 + 8 * 80 + 4 * 56 <= 20 * 96, "register
 static_assert(NTHREADS == 896 && 8 * 112 + 16 * 56 + 4 * 56 <= 28 * 72, "register shares");
 #endif
 constexpr int RAW_SLOT = ATP * HD + ATP * SCALE_ROW; // one tile of the widest format and its scales: 8704 bytes
-constexpr int NRAW = 8;
+constexpr int NRAW = 8;                     // packed tile slots: two side-groups (one being unpacked, one in flight)
+static_assert(NRAW % GT == 0, "whole groups only: a 7-slot ring, tried once, was 20 % slower and its results changed from run to run");
 constexpr int OP_SLOT = GP * 128 * 2;       // fp16 operand: 128 positions x 128 dims
 constexpr int NOP = 3;
 constexpr int NSB = 5;                      // S^T buffers: K runs NSB groups ahead of V
