@@ -6,3 +6,4 @@ without a GPU, but creating an Engine needs the built library and a CUDA device.
 from .engine import Engine, EngineError, lib_path, load_library, cap_T, NH, NKV, HD, MAXT  # noqa: F401
 from .build import build_library  # noqa: F401
 from . import parallel  # noqa: F401
+from . import cache_policy, conversation  # noqa: F401
