@@ -66,7 +66,9 @@ class KvConversation:
             if not self.eng.rewind_to(pos):
                 raise RuntimeError("rewind_to: no checkpoint at %d" % pos)
         else:
-            self.eng.reset()
+            # (cut to nothing rather than the engine's reset: that would also end a side request and drop what it keeps aside)
+            if self.eng.position() > 0:
+                self.eng.truncate(0)
             pos = 0
         del self.seq[pos:]
 
