@@ -155,3 +155,30 @@ def test_error_paths_keep_the_engine_usable(mk, torch_cuda):
     eng.sync()
     assert torch.isfinite(O).all()
     eng.close()
+
+
+def test_store_exhausted_in_the_middle_of_a_snapshot(mk, torch_cuda, monkeypatch):
+    """host_store.cu:246-266: a snapshot that runs out of store room half way gives its chunks back, the call answers "no
+    room" (-3 at the C ABI, None here), the sequence and the store are as before, and the same call succeeds once there is room"""
+    torch = torch_cuda
+    monkeypatch.setenv("MK_STORE_CHUNK_MIB", "1")
+    spec, win, L = "K*=5r,V*=6", 2048, 4100
+    eng = mk.Engine(2, L + 64, spec, win)
+    for layer in range(2):
+        fill_both(torch, eng, None, layer, 0, L, seed=layer)
+    eng.commit(L)
+    d0 = eng.state_digest()
+    need = eng.park_need(0)
+    assert need > (8 << 20)
+    eng.store_budget(5 << 20)  # five chunks: the snapshot takes them one by one and then finds no sixth
+    assert eng.park(0) is None
+    info = eng.store_info()
+    assert info["used"] == 0 and info["parked"] == 0
+    assert eng.position() == L and np.array_equal(eng.state_digest(), d0)
+    eng.store_budget(need + (2 << 20))
+    pid = eng.park(0)
+    assert pid and eng.park_bytes(pid) == need
+    eng.truncate(0)
+    eng.unpark(pid)
+    assert np.array_equal(eng.state_digest(), d0)
+    eng.close()
