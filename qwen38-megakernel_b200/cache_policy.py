@@ -52,6 +52,16 @@ class Parked:
     t: float = field(default_factory=time.time)
 
 
+@dataclass
+class Live:
+    """what the policy remembers about the engine's own conversation: its image spans, where its generation prompt starts (-1:
+    unknown), whether its last request had tools (None: unknown) and why it has low priority ("": it has not)"""
+    spans: list = field(default_factory=list)
+    gen: int = -1
+    tools: object = None
+    low: str = ""
+
+
 def common_prefix(a, b):
     n = 0
     for x, y in zip(a, b):
@@ -80,12 +90,18 @@ class ConversationCache:
         self.asst_marker = tuple(asst_marker)
         self.parked = {} if (limits.park_mib > 0 or limits.side_max > 0) else None  # id -> Parked, least recently parked first
         self.store_mib = limits.park_mib if limits.park_mib > 0 else SIDE_STORE_MIB
-        self.img_spans, self.live_gen, self.live_tools, self.live_low = [], -1, None, ""
+        self.live = Live()
         self.side, self.side_ready, self.answer_tokens = None, False, 0
         self.cache_pre, self.next_low, self.debris = "", "", None
         self.counters, self.store_gauge, self.rid = {}, (), 0
         self.lines = []
         self._log = log
+
+    # ---- the marks of the live conversation under the names the reference's server uses ----
+    img_spans = property(lambda self: self.live.spans, lambda self, v: setattr(self.live, "spans", v))
+    live_gen = property(lambda self: self.live.gen, lambda self, v: setattr(self.live, "gen", v))
+    live_tools = property(lambda self: self.live.tools, lambda self, v: setattr(self.live, "tools", v))
+    live_low = property(lambda self: self.live.low, lambda self, v: setattr(self.live, "low", v))
 
     # ---- small helpers ----
     def log(self, text):
@@ -100,8 +116,10 @@ class ConversationCache:
 
     def side_keep(self):
         """mk_srv_cache.py:30-34: a side request's own conversation is parked after it"""
-        a = self.args
-        return self.parked is not None and a.side_max > 0 and a.park_mib > 0 and bool(getattr(self.eng, "side_keep", False))
+        lim = self.args
+        if self.parked is None or lim.side_max <= 0 or lim.park_mib <= 0:
+            return False
+        return bool(getattr(self.eng, "side_keep", False))
 
     def _budget(self):
         return self.args.park_mib << 20
@@ -111,10 +129,10 @@ class ConversationCache:
 
     # ---- where a prompt would resume on a cached sequence (mk_srv_cache.py:37-53) ----
     def resume_point(self, seq, committed, cks, cached_spans, toks, spans):
-        """(common prefix, the image position that cut it or None, the position it resumes at, 'append' | 'checkpoint' | 'reset').
-        The last prompt token is always processed again; an image span present on one side only cuts the prefix at its start;
-        past the committed length the cached sequence continues by appending (not in exact mode), before it only a checkpoint
-        can be resumed."""
+        """Returns (tokens shared with the cache, position of the image span that shortened that or None, where the engine
+        would resume, how: 'append', 'checkpoint' or 'reset'). The last prompt token is always processed again; an image span
+        present on one side only cuts the prefix at its start; past the committed length the cached sequence continues by
+        appending (not in exact mode), before it only a checkpoint can be resumed."""
         match = min(common_prefix(seq, toks), len(toks) - 1)
         pos, cut = match, None
         for p, _, _ in set(spans) ^ set(cached_spans):
@@ -132,12 +150,12 @@ class ConversationCache:
     def cache_switch(self, toks, spans, first_turn, max_tokens=-1, tools=True):
         """Returns what was done, for the caller's log and the tests: 'side-resume', 'side', 'unpark', 'unpark+park', 'edit',
         'park', 'none'."""
-        eng, a = self.eng, self.args
-        self.cache_pre, self.next_low, self.debris = "", "", None
-        seq = eng.sequence()
-        live = self.resume_point(seq, eng.committed(), eng.checkpoints(), self.img_spans, toks, spans)
+        self.cache_pre = self.next_low = ""
+        self.debris = None
+        eng, a, seq = self.eng, self.args, self.eng.sequence()
+        live = self.resume_point(seq, eng.committed(), eng.checkpoints(), self.live.spans, toks, spans)
         lost = len(seq) - live[2]                                  # cached positions the plain path would throw away
-        continues = self.live_gen >= 0 and live[0] >= self.live_gen  # the prompt reaches the live one's generation prompt
+        continues = 0 <= self.live.gen <= live[0]                  # the prompt reaches the live one's generation prompt
         bounded = 0 < max_tokens <= SIDE_REPLY_MAX
         side_ok = (a.side_max > 0 and len(toks) <= a.side_max and not continues and lost >= max(2 * len(toks), a.park_min)
                    and (a.park_mib <= 0 or not tools or bounded))
@@ -163,18 +181,20 @@ class ConversationCache:
                     pick = (e, r)
             if pick:
                 e, r = pick
-                self.park_live(seq, "another conversation came back", keep=e.id, low=self.live_low)
+                self.park_live(seq, "another conversation came back", keep=e.id, low=self.live.low)
                 self.unpark(e)
-                if r[2] in e.pins and r[0] < e.gen:
-                    # only its pinned system prompt is shared: a new session; the restored one goes back to the store whole
-                    self.park_live(eng.sequence(), "a new session reuses its system prompt",
-                                   low="it was parked with low priority" if e.low else "")
-                    return "unpark+park"
-                return "unpark"
+                shares_only_pinned_head = r[2] in e.pins and r[0] < e.gen
+                if not shares_only_pinned_head:
+                    return "unpark"
+                # a new session on the same system prompt: the restored conversation goes back to the store whole
+                again_low = "it was parked with low priority" if e.low else ""
+                self.park_live(eng.sequence(), "a new session reuses its system prompt", low=again_low)
+                return "unpark+park"
 
         # 3. a first turn - or, with parking on, a request without tools that would displace a conversation with tools - runs
         #    beside the live conversation
-        if side_ok and (first_turn or (not tools and self.live_tools and a.park_mib > 0)):
+        beside_tools = bool(self.live.tools) and not tools and a.park_mib > 0
+        if side_ok and (first_turn or beside_tools):
             summary_like = not tools and len(toks) >= a.park_min and a.park_mib > 0
             self.side_start(seq, len(toks), max_tokens,
                             after="replaced right after a summary request beside it" if summary_like else "")
@@ -184,15 +204,18 @@ class ConversationCache:
         #    is that same conversation with its later history edited
         if a.park_mib > 0 and not continues and lost >= a.park_min:
             k = self.first_reply(toks)
-            if k is not None and live[0] >= k + len(self.asst_marker):
+            same_start = k is not None and k + len(self.asst_marker) <= live[0]
+            if same_start:
                 self.log("not parked: the prompt is the cached conversation with its history edited (it matches %d of the %d cached "
                          "tokens, past its first reply at %d)" % (live[0], len(seq), k))
                 return "edit"
-            debris = "" if (tools or not self.live_tools) else "replaced by a request without tools"
-            provisional = bool(debris) and not self.live_low
-            e = self.park_live(seq, "a new conversation", low=self.live_low or debris, provisional=provisional)
-            self.debris = e if provisional else None
-            self.next_low = debris and "the conversation of a request without tools that replaced one with tools"
+            debris = "replaced by a request without tools" if (self.live.tools and not tools) else ""
+            provisional = bool(debris) and not self.live.low
+            entry = self.park_live(seq, "a new conversation", low=self.live.low or debris, provisional=provisional)
+            if provisional:
+                self.debris = entry
+            if debris:
+                self.next_low = "the conversation of a request without tools that replaced one with tools"
             return "park"
         return "none"
 
@@ -234,10 +257,10 @@ class ConversationCache:
         return True
 
     def evict(self, pid, why):
-        e = self.parked.pop(pid)
         self.eng.park_drop(pid)
-        self.count(park_evictions=1)
+        e = self.parked.pop(pid)
         self.store_update()
+        self.count(park_evictions=1)
         self.log("evicted the parked conversation of %d tokens (%s; %s)" % (len(e.seq), _mib(e.nbytes), why))
 
     # ---- park / unpark (mk_srv_cache.py:178-235) ----
@@ -259,13 +282,17 @@ class ConversationCache:
                 return None
         else:
             self.make_room(need, budget, keep)
-        pins = list(eng.pinned()) if a.park_cks > 0 and getattr(eng, "ck_pins", False) else []
-        cks = sorted(set(sorted(eng.checkpoints())[-a.park_cks:]) | set(pins)) if a.park_cks > 0 else []
+        pins, cks = [], []
+        if a.park_cks > 0:  # what the engine parks: the newest park_cks checkpoints and the pinned ones
+            if getattr(eng, "ck_pins", False):
+                pins = list(eng.pinned())
+            newest = sorted(eng.checkpoints())[-a.park_cks:]
+            cks = sorted(set(newest).union(pins))
         pid = eng.park(a.park_cks)
         if pid is None:
             self.log("not parked: no room in the host store for the cached %d tokens (%s)" % (len(seq), _mib(need)))
             return None
-        e = Parked(pid, list(seq), cks, eng.committed(), self.img_spans, self.live_gen, need, low=bool(low), tools=self.live_tools,
+        e = Parked(pid, list(seq), cks, eng.committed(), self.live.spans, self.live.gen, need, low=bool(low), tools=self.live.tools,
                    pins=tuple(pins))
         self.parked[pid] = e
         info = self.store_update()
@@ -277,15 +304,17 @@ class ConversationCache:
 
     def unpark(self, e):
         """the engine becomes parked conversation e; its entry is freed (also when the engine fails: then the error goes on)"""
+        failed = None
         try:
             self.eng.unpark(e.id)
-        except RuntimeError:
-            self.parked.pop(e.id, None)
-            self.eng.park_drop(e.id)
+        except RuntimeError as err:
+            failed = err
+        self.parked.pop(e.id, None)
+        if failed is not None:
+            self.eng.park_drop(e.id)  # (the entry goes too, with its host memory)
             self.store_update()
-            raise
-        del self.parked[e.id]
-        self.img_spans, self.live_gen, self.live_tools, self.live_low = e.img_spans, e.gen, e.tools, ""
+            raise failed
+        self.live = Live(e.img_spans, e.gen, e.tools, "")
         self.store_update()
         self.count(park_restores=1)
         self.cache_pre = "restored a parked conversation (%d tokens); " % len(e.seq)
@@ -311,7 +340,8 @@ class ConversationCache:
         if not eng.side_begin():
             self.log("side request: no room in the host store: the cached %d tokens are not kept" % len(seq))
             return
-        self.side = (len(seq), self.img_spans, self.live_gen, self.live_tools, self.live_low, after)
+        self.side = (len(seq), self.live, after)  # the kept conversation's marks come back with it
+        self.live = Live(self.live.spans, self.live.gen, self.live.tools, self.live.low)
         self.side_ready = False
         self.count(side_requests=1)
         self.cache_pre = "side request: the cached %d tokens are kept aside; " % len(seq)
@@ -321,31 +351,42 @@ class ConversationCache:
             self.log("side request: no room in the host store to continue its parked conversation of %d tokens" % len(resume.seq))
             return
         del self.parked[resume.id]
-        self.img_spans, self.live_gen, self.live_tools = resume.img_spans, resume.gen, resume.tools
+        self.live.spans, self.live.gen, self.live.tools = resume.img_spans, resume.gen, resume.tools
         self.store_update()
         self.count(side_resumed=1)
         self.cache_pre += "its parked conversation (%d tokens) restored; " % len(resume.seq)
 
+    def _side_conversation_to_park(self):
+        """what the engine holds at the end of a side request, if it is worth parking (side_keep(), its prompt was processed and a
+        checkpoint exists to resume from), with room made for it among side and low-priority entries only: (fields of its Parked
+        entry or None, whether it fits)"""
+        eng = self.eng
+        if not (self.side_keep() and self.side_ready and eng.checkpoints()):
+            return None, True
+        kept_sides = [pid for pid, e in self.parked.items() if e.side]  # least recently parked first
+        for pid in kept_sides[:max(0, len(kept_sides) - SIDE_KEEP_MAX + 1)]:
+            self.evict(pid, "the oldest of %d kept side request conversations" % SIDE_KEEP_MAX)
+        nbytes = eng.park_need(SIDE_PARK_CKS)
+        own = dict(seq=list(eng.sequence()), cks=sorted(eng.checkpoints())[-SIDE_PARK_CKS:], committed=eng.committed(),
+                   img_spans=self.live.spans, gen=self.live.gen, nbytes=nbytes)
+        fits = nbytes <= self._budget() and self.make_room(nbytes, self._budget(), side_only=True)
+        return own, fits
+
     def side_finish(self):
-        """After a side request, also a failed one: the kept sequence comes back; with side_keep() the side request's own
-        conversation is parked first when its prompt was processed and it has a checkpoint to resume from."""
+        """Ends a side request, also a failed one or one whose client left (mk_srv_cache.py:267-317). Three outcomes: the kept
+        conversation is the engine's again (its marks with it; the side request's own conversation parked before, if
+        _side_conversation_to_park says so); the store ran full while the side request's conversation was being parked, so that one
+        stays the engine's; or nothing is left and the next request prefills in full."""
         if self.side is None:
             return
-        n, spans, gen, tools, low, after = self.side
+        n_kept, kept_marks, after = self.side
         self.side = None
-        eng, a = self.eng, self.args
-        back, pid, own, room = False, None, None, True
+        eng = self.eng
+        back, pid, own, fits = False, None, None, True
         try:
             if eng.side_active():
-                if self.side_keep() and self.side_ready and eng.checkpoints():
-                    sides = [p for p, e in self.parked.items() if e.side]
-                    for p in sides[:max(0, len(sides) - SIDE_KEEP_MAX + 1)]:
-                        self.evict(p, "the oldest of %d kept side request conversations" % SIDE_KEEP_MAX)
-                    own = dict(seq=list(eng.sequence()), cks=sorted(eng.checkpoints())[-SIDE_PARK_CKS:], committed=eng.committed(),
-                               img_spans=self.img_spans, gen=self.live_gen, nbytes=eng.park_need(SIDE_PARK_CKS))
-                    # (other kinds of parked conversations are not evicted for it)
-                    room = own["nbytes"] <= self._budget() and self.make_room(own["nbytes"], self._budget(), side_only=True)
-                if own is not None and room:
+                own, fits = self._side_conversation_to_park()
+                if own is not None and fits:
                     back, pid = eng.side_end_park(SIDE_PARK_CKS)
                 else:
                     back = eng.side_end()
@@ -353,36 +394,42 @@ class ConversationCache:
             self.log("side request: %s" % err)
             eng.side_drop()
             own = None
-        self.store_update()
         if pid:
-            self.parked[pid] = Parked(pid, side=True, tools=self.live_tools, **own)
-            self.store_update()
+            self.parked[pid] = Parked(pid, side=True, tools=self.live.tools, **own)
             self.count(side_kept=1)
+        self.store_update()
         if back:
-            self.img_spans, self.live_gen, self.live_tools = spans, gen, tools
-            self.live_low = after if after and self.answer_tokens >= SUMMARY_ANSWER_MIN else low
-            self.log("side request done: the cached %d tokens are back%s" % (
-                n, "; its own conversation (%d tokens) parked" % len(own["seq"]) if pid else
-                "; its own conversation was not parked (no room in the host store)" if own is not None else ""))
-        elif own is not None and room:
-            # side_end_park lost the kept sequence; the side request's conversation stays the engine's
-            self.count(side_dropped=1)
+            summary = bool(after) and self.answer_tokens >= SUMMARY_ANSWER_MIN
+            self.live = Live(kept_marks.spans, kept_marks.gen, kept_marks.tools, after if summary else kept_marks.low)
+            note = ""
+            if pid:
+                note = "; its own conversation (%d tokens) parked" % len(own["seq"])
+            elif own is not None:
+                note = "; its own conversation was not parked (no room in the host store)"
+            self.log("side request done: the cached %d tokens are back%s" % (n_kept, note))
+            return
+        self.count(side_dropped=1)
+        if own is not None and fits:
+            # side_end_park lost the kept sequence; the side request's conversation stays the engine's, with its marks
             self.log("side request: the cached %d tokens were dropped (the host store ran full): the side request's own conversation "
-                     "(%d tokens) stays cached" % (n, len(own["seq"])))
-        else:
-            self.img_spans, self.live_gen, self.live_tools, self.live_low = [], -1, None, ""
-            self.count(side_dropped=1)
-            self.log("side request: the cached %d tokens were dropped (the host store ran full, or an engine error): the next request "
-                     "prefills its prompt in full" % n)
+                     "(%d tokens) stays cached" % (n_kept, len(own["seq"])))
+            return
+        self.live = Live()
+        self.log("side request: the cached %d tokens were dropped (the host store ran full, or an engine error): the next request "
+                 "prefills its prompt in full" % n_kept)
 
     # ---- a provisional low-priority mark (mk_srv_cache.py:319-332) ----
     def debris_finish(self, replied):
         """The conversation with tools that a request without tools replaced was parked with a provisional low-priority mark;
         a reply shorter than a summary's takes the mark back (a title or tags task quoted it). The mark stays after a long
         answer and without a reply."""
-        e, self.debris = self.debris, None
-        if e is None or not replied or self.answer_tokens >= SUMMARY_ANSWER_MIN or self.parked.get(e.id) is not e:
+        entry = self.debris
+        self.debris = None
+        if entry is None or not replied:
             return
+        if self.answer_tokens >= SUMMARY_ANSWER_MIN or self.parked.get(entry.id) is not entry:
+            return
+        e = entry
         e.low = False
         self.store_update()
         self.log("the parked conversation of %d tokens keeps normal priority: the request answered in %d tokens (< %d: not a summary)"
