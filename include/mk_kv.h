@@ -55,7 +55,10 @@ int mk_kv_sync(void * h);
  * status word mk_kv_sync reports, stops waiting, lets its copies in flight land, frees its tensor memory and returns. These calls
  * set the limits for the launches that follow, process-wide (defaults: 10,000 ns, 200,000, 2,097,152: about two seconds;
  * (0, 0, 0) restores them). mk_kv_wait_limits_expire_now makes the first wait that does not succeed at once give up: the
- * failure-path test uses it (nothing traps or hangs: the kernel returns with a wrong result the host rejects). */
+ * failure-path test uses it (nothing traps or hangs: the kernel returns with a wrong result the host rejects). The limits are the
+ * tensor-core kernel's; the mma.sync kernel (MK_KV_ATTN=fast, and the fallback of the batched and no-allocation calls) has one
+ * compiled-in limit of 8,388,608 tries per wait (seconds) and no early expiry: it does not wait for copies in flight before it
+ * returns, which is safe only because no copy is still in flight after seconds. */
 int mk_kv_wait_limits(unsigned hint_ns, unsigned rounds, unsigned polls);
 int mk_kv_wait_limits_expire_now(void);
 

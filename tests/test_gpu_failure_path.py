@@ -13,8 +13,11 @@ from gpu_util import TOL, attend_both, fill_both
 pytestmark = pytest.mark.gpu
 
 
-def test_expired_wait_returns_error_and_engine_stays_usable(mk, torch_cuda):
+def test_expired_wait_returns_error_and_engine_stays_usable(mk, torch_cuda, monkeypatch):
     torch = torch_cuda
+    # the limits are the tensor-core kernel's (read when the engine is made); the mma.sync kernel's are compiled in: seconds, by
+    # which every copy it issued has landed, so it is never made to give up early
+    monkeypatch.setenv("MK_KV_ATTN", "tc")
     spec, win, L, T = "K*=5r,V*=6", 2048, 9000, 8
     eng = mk.Engine(1, L + 64, spec, win)
     orc = ko.Cache(1, L + 64, spec, win)
