@@ -31,6 +31,7 @@
 // Every wait is bounded (about two seconds by default; the limits are launch arguments), then the status word and a CTA-wide
 // flag are set, no later wait of the CTA blocks, the producer waits (bounded) for its copies still in flight, and the kernel
 // runs to its end and frees its tensor memory.
+#include <algorithm>
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
@@ -322,7 +323,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
         const AttnJob * Jp = &a.one;
         if (a.jobs) { // batch mode: the job whose items contain this CTA
             int j = 0;
-            while (j + 1 < a.njobs && (int) blockIdx.x >= a.jobs[j + 1].item0) j++;
+            while (j + 1 < a.njobs && (int) blockIdx.x >= a.jobs[j + 1].titem0) j++;
             Jp = &a.jobs[j];
         }
         const unsigned * src = reinterpret_cast<const unsigned *>(Jp);
@@ -353,20 +354,31 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
     const unsigned tb = sm.tmem_base;
     const AttnJob & J = sm.job;
     const KvView & kv = J.kv;
-    // spread mode: CTA kk of kv head g runs tasks kk, kk + cph, .. of the head; batch mode: the CTA runs the groups of chunk c_fixed
-    // of kv head g of its job in order (task t = group t), the running max carried from group to group in registers
+    // spread mode: CTA kk of kv head g runs tasks kk, kk + cph, .. of the head; batch mode: the CTA runs the groups of chunks c_first
+    // .. c_first + cpi - 1 of kv head g of its job in order, chunk after chunk, the running max carried from group to group in
+    // registers and started anew with every chunk; its partial is the head's slot number ci
     const bool batch = a.jobs != nullptr;
-    const int item = batch ? (int) blockIdx.x - J.item0 : 0;
-    const int g = batch ? item / J.nch : (int) blockIdx.x / a.cph, kk = batch ? 0 : (int) blockIdx.x % a.cph, slot = blockIdx.x;
-    const int c_fixed = batch ? item % J.nch : 0, tstep = batch ? 1 : a.cph;
+    const int cpi = batch ? max(J.cpi, 1) : 1, nit = batch ? (J.nch + cpi - 1) / cpi : 1;
+    const int item = batch ? (int) blockIdx.x - J.titem0 : 0, ci = item % nit;
+    const int g = batch ? item / nit : (int) blockIdx.x / a.cph, kk = batch ? 0 : (int) blockIdx.x % a.cph;
+    const int slot = batch ? J.item0 + g * J.nch + ci : (int) blockIdx.x;
+    const int c_first = ci * cpi, c_count = batch ? min(cpi, J.nch - c_first) : 0, tstep = batch ? 1 : a.cph;
     const int T = J.T, n = J.n, R = GQ * T, ws = J.ws;
     Geo4 geo4;
     geo4.g = make_geo(J, GT);
     geo4.mul_nch = geo4.g.nch > 1 ? 0xffffffffu / (unsigned) geo4.g.nch + 1u : 0u;
     geo4.mul_nch1 = geo4.g.nch > 2 ? 0xffffffffu / (unsigned) (geo4.g.nch - 1) + 1u : 0u;
     const AttnTask * const ttab = a.tasks;
-    const int t_end = batch ? ((c_fixed == geo4.g.nch - 1 ? geo4.g.nt_last : geo4.g.nt_full) + GT - 1) / GT : ttab ? a.ntasks : geo4.g.ntasks_head;
-    auto get_task = [&](int t) -> Task { return batch ? make_task(geo4.g, GT, 1, t, c_fixed) : ttab ? ttab[t] : make_task4(geo4, t); };
+    // (batch mode: every chunk has nb_full groups but the job's last one, which is the last of its CTA too)
+    const int t_end = batch ? c_count * geo4.g.nb_full - (c_first + c_count == geo4.g.nch ? geo4.g.nb_full - geo4.g.nb_last : 0)
+                            : ttab ? a.ntasks : geo4.g.ntasks_head;
+    auto get_task = [&](int t) -> Task {
+        if (batch) {
+            const int cc = t / geo4.g.nb_full;
+            return make_task(geo4.g, GT, 1, t - cc * geo4.g.nb_full, c_first + cc);
+        }
+        return ttab ? ttab[t] : make_task4(geo4, t);
+    };
     const int G = kk < t_end ? (t_end - kk + tstep - 1) / tstep : 0; // this CTA's groups: tasks kk, kk + tstep, ..
 
     // The kv head's query rows come staged (qprep: fp16 -> fp32 -> K's rotation -> x 1/16 -> fp16 in the K-major B operand's layout,
@@ -1098,10 +1110,17 @@ cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * job
     TcKernel kern = tc_kernel_for(jobs_host[0].kv.s[0].bits, jobs_host[0].kv.s[1].bits);
     for (int j = 1; j < njobs; j++)
         if (jobs_host[j].kv.s[0].bits != jobs_host[0].kv.s[0].bits || jobs_host[j].kv.s[1].bits != jobs_host[0].kv.s[1].bits) kern = tc::attn_tc_kernel<0, 0>;
-    kern<<<total_items, tc::NTHREADS, attend_tc_smem_bytes(), stream>>>(a);
+    int grid = 0; // (the jobs' CTAs as step_batch planned them: titem0, cpi)
+    for (int j = 0; j < njobs; j++) {
+        const int cpi = std::max(jobs_host[j].cpi, 1);
+        if (jobs_host[j].titem0 != grid) return cudaErrorInvalidValue;
+        grid += NKV * ((jobs_host[j].nch + cpi - 1) / cpi);
+    }
+    if (grid > total_items) return cudaErrorInvalidValue;
+    kern<<<grid, tc::NTHREADS, attend_tc_smem_bytes(), stream>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return launch_merge(jobs_dev, jobs_host, njobs, max_T, part, ml, stream);
+    return launch_merge(jobs_dev, jobs_host, njobs, max_T, part, ml, stream, nullptr, nullptr, true);
 }
 
 } // namespace mkkv

@@ -586,6 +586,8 @@ AttnJob KvEngine::whole_job(const Seq & s, const char * what, int layer, int n, 
     attn_dims(n + T, j.nch, j.cs);
     j.ws = kv_ws(n + T, cfg_.win);
     j.item0 = 0;
+    j.cpi = 1;
+    j.titem0 = 0;
     j.pos_lo = 0;
     j.pos_hi = n + T;
     j.pstride = 1;
@@ -650,6 +652,8 @@ void KvEngine::attend_partial_impl(int seq, int layer, int n, int T, const void 
     attn_dims(L, j.nch, j.cs);
     j.ws = kv_ws(L, cfg_.win);
     j.item0 = 0;
+    j.cpi = 1;
+    j.titem0 = 0;
     j.pos_lo = pos_lo;
     j.pos_hi = pos_hi;
     j.pstride = 1;
@@ -717,6 +721,8 @@ void KvEngine::combine(int layer, int T, int nparts, const void * parts, const v
     j.cs = 0;
     j.ws = 0;
     j.item0 = 0;
+    j.cpi = 1;
+    j.titem0 = 0;
     j.pos_lo = j.pos_hi = 0;
     j.pstride = NKV; // partial p of kv head g is slot p * 4 + g
     j.rstride = 0;
@@ -787,6 +793,8 @@ void KvEngine::combine_layers(int nlayers, int T, int nparts, const void * parts
         j.cs = 0;
         j.ws = 0;
         j.item0 = l * NKV;          // partial p of kv head g of layer l is slot (p * nlayers + l) * 4 + g
+        j.cpi = 1;
+        j.titem0 = 0;
         j.pos_lo = j.pos_hi = 0;
         j.pstride = nlayers * NKV;
         j.rstride = (long long) (rank_stride / 4); // (0: the ranks' arrays lie one after another)
@@ -821,7 +829,7 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
     // the job tables are reused by every call: the previous call's upload must have been consumed
     MKKV_CK(cudaEventSynchronize(ev_compute_));
     AppendJob * aj = static_cast<AppendJob *>(h_ajobs_);
-    int items = 0, maxT = 0;
+    int items = 0, tc_items = 0, maxT = 0;
     size_t row = 0;
     for (int j = 0; j < njobs; j++) {
         Seq & s = seq_ref(seqs[j]);
@@ -840,6 +848,15 @@ void KvEngine::step_batch(int njobs, const int * seqs, int layer, const int * n,
         a.item0 = items;
         if (use_tc_ && j < qprep_slots_) a.Qp = qprep_ + (size_t) j * NKV * (QP_HEAD_BYTES / 2); // (staged below, every job in one launch)
         items += NKV * a.nch;
+        // the tensor-core kernel's CTAs: a CTA costs about two groups' time besides its groups, so chunks of fewer than
+        // TC_ITEM_GROUPS groups of 128 positions share one (the long sequences' chunks stay one per CTA: they balance the SMs).
+        // 32 sequences of 2,000 .. 100,000 positions, tokens per second: 13.2 k with one chunk per CTA, 14.2 k / 14.4 k / 14.7 k /
+        // 14.5 k with 8 / 12 / 16 / 24 groups
+        constexpr int TC_ITEM_GROUPS = 16;
+        const int nb_full = (a.cs / ATP + 3) / 4;
+        a.cpi = std::max(1, std::min(a.nch, (TC_ITEM_GROUPS + nb_full - 1) / std::max(nb_full, 1)));
+        a.titem0 = tc_items;
+        tc_items += NKV * ((a.nch + a.cpi - 1) / a.cpi);
         maxT = std::max(maxT, T[j]);
         aj[j].kv = a.kv;
         aj[j].K = static_cast<const uint16_t *>(K) + row * NKV * HD;

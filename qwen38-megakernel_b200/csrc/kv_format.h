@@ -79,6 +79,9 @@ struct AttnJob {
     int n, T;
     int nch, cs, ws;    // partition and window start of L = n + T
     int item0;          // first (kv head, chunk) item of this job in the call's partial buffers
+    int cpi, titem0;    // the tensor-core kernel's batch mode: a CTA runs cpi consecutive chunks of a kv head (short chunks are not
+                        // worth a CTA each), so a head has ceil(nch / cpi) partials, in slots item0 + g nch + 0 ..; titem0: the job's
+                        // first CTA in that grid. cpi <= 1: one chunk per CTA
     int pos_lo, pos_hi; // only positions in [pos_lo, pos_hi) are attended (multiples of 32 or the context end; whole context: 0, n + T)
     int pstride;        // merge: partial c of kv head g is slot item0 + g nch + c (pstride 1), else item0 + c pstride + g
     long long rstride;  // merge, pstride > 1 only: floats between partial c and c + 1 of both arrays when they are not pstride

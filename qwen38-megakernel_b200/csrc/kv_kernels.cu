@@ -266,7 +266,7 @@ cudaError_t launch_gather(const CopyRegion * regions, int nregions, int a, int b
 
 // merge of the chunk partials of one (query head, token), one warp per row (kv_merge.cuh)
 __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__ AttnArgs a, int rows_per_job, int raw, float * part_out,
-                                                         float2 * ml_out) {
+                                                         float2 * ml_out, int grouped) {
     const int lane = threadIdx.x & 31, idx = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int j = idx / rows_per_job, rr = idx % rows_per_job;
     if (j >= (a.jobs ? a.njobs : 1)) return;
@@ -277,12 +277,14 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const __grid_constant__
     const size_t cstep = J.pstride > 1 ? (size_t) J.pstride : 1; // slots between consecutive partials of the kv head
     // (partials beyond 64 per kv head do not occur: nch <= 20, or #SM / 4 for the spread kernels)
     const bool packed = J.pstride > 1 && J.rstride != 0;
-    merge_row(J, a.part, a.ml, i0, packed ? (size_t) J.rstride : cstep * AR * HD, packed ? (size_t) J.rstride / 2 : cstep * AR, J.nch, h, t, lane, raw, part_out,
+    // (grouped: the tensor-core kernel's batch mode left one partial per cpi chunks)
+    const int count = grouped && J.cpi > 1 ? (J.nch + J.cpi - 1) / J.cpi : J.nch;
+    merge_row(J, a.part, a.ml, i0, packed ? (size_t) J.rstride : cstep * AR * HD, packed ? (size_t) J.rstride / 2 : cstep * AR, count, h, t, lane, raw, part_out,
               ml_out);
 }
 
 cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,
-                         cudaStream_t stream, float * raw_part, float2 * raw_ml) {
+                         cudaStream_t stream, float * raw_part, float2 * raw_ml, bool grouped) {
     AttnArgs a;
     a.one = jobs_host[0];
     a.jobs = njobs > 1 ? jobs_dev : nullptr;
@@ -290,7 +292,7 @@ cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, in
     a.part = part;
     a.ml = ml;
     const int rows_per_job = NH * max_T;
-    attn_merge_kernel<<<(njobs * rows_per_job + 7) / 8, 256, 0, stream>>>(a, rows_per_job, raw_part ? 1 : 0, raw_part, raw_ml);
+    attn_merge_kernel<<<(njobs * rows_per_job + 7) / 8, 256, 0, stream>>>(a, rows_per_job, raw_part ? 1 : 0, raw_part, raw_ml, grouped ? 1 : 0);
     return cudaGetLastError();
 }
 
@@ -352,6 +354,8 @@ cudaError_t launch_attend_static(const AttnJob & job, int * status, cudaStream_t
     if (!part || !ml) return cudaErrorInitializationError; // (no engine was constructed on this device)
     AttnJob j = job;
     j.item0 = 0;
+    j.cpi = 1;
+    j.titem0 = 0;
     // every partial row the merge reads is written by the split kernel of the same call: nothing has to start at zero.
     // One CTA per (kv head, chunk): that mode of the mma.sync kernel needs no other scratch than the partials.
     return launch_attend_fast(nullptr, &j, 1, NKV * j.nch, j.T, 0, part, ml, STATIC_ITEMS, nullptr, 0, 0, status, nullptr, false, stream);

@@ -21,11 +21,12 @@ cudaError_t launch_spill(const KvView * views, int layers, int p0, int p1, cudaS
 // ring rows of positions [p0, p1) rebuilt from the main rows (after a rewind), all layers of one sequence
 cudaError_t launch_refill(const KvView * views, int layers, int p0, int p1, cudaStream_t stream);
 
-// the merge alone: job j's partials are slots item0 + g nch .. + nch - 1 of kv head g
+// the merge alone: job j's partials are slots item0 + g nch .. + nch - 1 of kv head g (grouped: .. + ceil(nch / cpi) - 1, as the
+// tensor-core kernel's batch mode leaves them)
 // raw_part / raw_ml (one job only): write the merged but un-normalised result as one partial per kv head, [4][48][256] floats and
 // [4][48] (m, l), instead of the job's O
 cudaError_t launch_merge(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int max_T, float * part, float2 * ml,
-                         cudaStream_t stream, float * raw_part = nullptr, float2 * raw_ml = nullptr);
+                         cudaStream_t stream, float * raw_part = nullptr, float2 * raw_ml = nullptr, bool grouped = false);
 // mma.sync path (kv_attend_fast.cu). One job: cooperative launch over num_sms CTAs with an
 // exchange of row maxima through xmax ([4][20][nbmax][48] 8-byte words {epoch, value}, zeroed once; epoch must be non-zero and
 // differ from every earlier launch's). Several jobs: one CTA per (job, kv head, chunk). part / ml hold part_slots partials.
