@@ -26,8 +26,8 @@
 //     and no per-tile accumulator rescale is needed;
 //   - a CTA writes one un-normalised partial (m, l, O); when the CTAs of a kv head have all written theirs (arrival count,
 //     bounded wait) each merges one or two of the head's rows in the kernel's tail, four warps to a row;
-//   - batch mode (several jobs): one CTA per (job, kv head, chunk) in a plain launch, the chunk's groups in order on that CTA with
-//     the running max carried in registers; attn_merge_kernel afterwards.
+//   - batch mode (several jobs): one CTA per (job, kv head, run of cpi chunks) in a plain launch, the chunks' groups in order on
+//     that CTA with the running max carried in registers and started anew at every chunk; attn_merge_kernel afterwards.
 // Every wait is bounded (about two seconds by default; the limits are launch arguments), then the status word and a CTA-wide
 // flag are set, no later wait of the CTA blocks, the producer waits (bounded) for its copies still in flight, and the kernel
 // runs to its end and frees its tensor memory.
@@ -121,7 +121,7 @@ struct Smem {
 
 struct Args {
     AttnJob one;
-    const AttnJob * jobs;   // batch mode: device array of njobs jobs, one CTA per (job, kv head, chunk); else null: one job spread
+    const AttnJob * jobs;   // batch mode: device array of njobs jobs, one CTA per (job, kv head, cpi chunks); else null: one job spread
     int njobs;              // over cph CTAs per kv head with the exchange of row maxima
     int cph, ntasks;        // CTAs per kv head; tasks per kv head when a host-built list is given
     const AttnTask * tasks; // optional list (position-range jobs)
@@ -1076,8 +1076,8 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
     return launch_merge(nullptr, &merge_job, 1, job.T, part, ml, stream, raw_part, raw_ml);
 }
 
-// Batch mode: njobs jobs, one CTA per (job, kv head, chunk) item in a plain launch (no CTA waits for another: the groups of a chunk
-// run in order on one CTA), then the merge kernel over the jobs' partials (slot = item).
+// Batch mode: njobs jobs, one CTA per (job, kv head, run of the job's cpi chunks) in a plain launch (no CTA waits for another: the
+// groups of a chunk run in order on one CTA), then the merge kernel over the jobs' partials (a head's partials: its first slots).
 cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
                                    float2 * ml, int part_slots, int * status, cudaStream_t stream) {
     if (njobs < 1 || total_items < 1 || total_items > part_slots || !jobs_dev) return cudaErrorNotSupported;

@@ -55,7 +55,7 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
                              const AttnTask * tasks_dev = nullptr, int ntasks = 0, int tasks_B = 0, float * raw_part = nullptr,
                              float2 * raw_ml = nullptr, unsigned long long * prof = nullptr, unsigned * done = nullptr,
                              unsigned * done_seq = nullptr);
-// batch mode of the same kernel: one CTA per (job, kv head, chunk) item, plain launch, then the merge kernel
+// batch mode of the same kernel: one CTA per (job, kv head, run of AttnJob::cpi chunks), plain launch, then the merge kernel
 cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * jobs_host, int njobs, int total_items, int max_T, float * part,
                                    float2 * ml, int part_slots, int * status, cudaStream_t stream);
 size_t attend_tc_smem_bytes();
