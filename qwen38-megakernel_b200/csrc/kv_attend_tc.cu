@@ -310,7 +310,10 @@ __device__ __forceinline__ Task make_task4(const Geo4 & G4, int t) {
 
 // KB / VB: the bits of the K / V main rows the instance is compiled for (0: any, decided per tile at run time). A compiled-in
 // format leaves two unpack bodies per side (the format and the q8_0 ring) instead of five: a smaller instruction footprint.
-template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_constant__ Args a) {
+// BATCH: the instance for several jobs (one CTA per job, kv head and run of chunks, no exchange between CTAs); the instance for one
+// job spread over the SMs carries none of that mode's code (with both modes in one body the spread mode's loops came out 1.7 %
+// slower).
+template <int KB, int VB, bool BATCH> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc_kernel(const __grid_constant__ Args a) {
     // (the dynamic shared memory starts on a 128-byte boundary -- there is no static shared memory in this kernel --, which is all the
     // bulk copies, matrix descriptors and barriers need; no pointer arithmetic here, so every access below is a shared-space one)
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -321,7 +324,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
 #endif
     {
         const AttnJob * Jp = &a.one;
-        if (a.jobs) { // batch mode: the job whose items contain this CTA
+        if (BATCH) { // the job whose items contain this CTA
             int j = 0;
             while (j + 1 < a.njobs && (int) blockIdx.x >= a.jobs[j + 1].titem0) j++;
             Jp = &a.jobs[j];
@@ -357,7 +360,7 @@ template <int KB, int VB> __global__ void __launch_bounds__(NTHREADS, 1) attn_tc
     // spread mode: CTA kk of kv head g runs tasks kk, kk + cph, .. of the head; batch mode: the CTA runs the groups of chunks c_first
     // .. c_first + cpi - 1 of kv head g of its job in order, chunk after chunk, the running max carried from group to group in
     // registers and started anew with every chunk; its partial is the head's slot number ci
-    const bool batch = a.jobs != nullptr;
+    constexpr bool batch = BATCH;
     const int cpi = batch ? max(J.cpi, 1) : 1, nit = batch ? (J.nch + cpi - 1) / cpi : 1;
     const int item = batch ? (int) blockIdx.x - J.titem0 : 0, ci = item % nit;
     const int g = batch ? item / nit : (int) blockIdx.x / a.cph, kk = batch ? 0 : (int) blockIdx.x % a.cph;
@@ -982,15 +985,24 @@ static_assert(sizeof(tc::Smem) + 128 <= 232448, "shared memory of one CTA");
 size_t attend_tc_smem_bytes() { return sizeof(tc::Smem) + 128; }
 // the kernel instance for a job's main formats: the served presets are compiled in, anything else runs the any-format instance
 typedef void (*TcKernel)(const tc::Args);
-static TcKernel tc_kernel_for(int kb, int vb) {
-    if (kb == 5 && vb == 6) return tc::attn_tc_kernel<5, 6>;
-    if (kb == 5 && vb == 5) return tc::attn_tc_kernel<5, 5>;
-    if (kb == 6 && vb == 5) return tc::attn_tc_kernel<6, 5>;
-    if (kb == 8 && vb == 8) return tc::attn_tc_kernel<8, 8>;
-    return tc::attn_tc_kernel<0, 0>;
+static TcKernel tc_kernel_for(int kb, int vb, bool batch) {
+    if (batch) {
+        if (kb == 5 && vb == 6) return tc::attn_tc_kernel<5, 6, true>;
+        if (kb == 5 && vb == 5) return tc::attn_tc_kernel<5, 5, true>;
+        if (kb == 6 && vb == 5) return tc::attn_tc_kernel<6, 5, true>;
+        if (kb == 8 && vb == 8) return tc::attn_tc_kernel<8, 8, true>;
+        return tc::attn_tc_kernel<0, 0, true>;
+    }
+    if (kb == 5 && vb == 6) return tc::attn_tc_kernel<5, 6, false>;
+    if (kb == 5 && vb == 5) return tc::attn_tc_kernel<5, 5, false>;
+    if (kb == 6 && vb == 5) return tc::attn_tc_kernel<6, 5, false>;
+    if (kb == 8 && vb == 8) return tc::attn_tc_kernel<8, 8, false>;
+    return tc::attn_tc_kernel<0, 0, false>;
 }
-static const TcKernel tc_kernels[] = {tc::attn_tc_kernel<5, 6>, tc::attn_tc_kernel<5, 5>, tc::attn_tc_kernel<6, 5>, tc::attn_tc_kernel<8, 8>,
-                                      tc::attn_tc_kernel<0, 0>};
+static const TcKernel tc_kernels[] = {tc::attn_tc_kernel<5, 6, false>, tc::attn_tc_kernel<5, 5, false>, tc::attn_tc_kernel<6, 5, false>,
+                                      tc::attn_tc_kernel<8, 8, false>, tc::attn_tc_kernel<0, 0, false>,
+                                      tc::attn_tc_kernel<5, 6, true>,  tc::attn_tc_kernel<5, 5, true>,  tc::attn_tc_kernel<6, 5, true>,
+                                      tc::attn_tc_kernel<8, 8, true>,  tc::attn_tc_kernel<0, 0, true>};
 // every instance may use the CTA's full shared memory (set once per device)
 static cudaError_t tc_prepare() {
     static bool attr_set[64] = {};
@@ -1064,7 +1076,7 @@ cudaError_t launch_attend_tc(const AttnJob & job, int num_sms, float * part, flo
     a.done = fused ? done : nullptr;
     a.done_target = fused ? (*done_seq + 1u) * (unsigned) a.cph : 0u;
     void * args[] = {&a};
-    e = cudaLaunchCooperativeKernel((const void *) tc_kernel_for(job.kv.s[0].bits, job.kv.s[1].bits), dim3(NKV * a.cph), dim3(tc::NTHREADS), args, attend_tc_smem_bytes(), stream);
+    e = cudaLaunchCooperativeKernel((const void *) tc_kernel_for(job.kv.s[0].bits, job.kv.s[1].bits, false), dim3(NKV * a.cph), dim3(tc::NTHREADS), args, attend_tc_smem_bytes(), stream);
     if (e != cudaSuccess) return e;
     if (fused) {
         *done_seq += 1u;
@@ -1107,9 +1119,9 @@ cudaError_t launch_attend_tc_batch(const AttnJob * jobs_dev, const AttnJob * job
     cudaError_t e = tc_prepare();
     if (e != cudaSuccess) return e;
     // (the jobs of one batch may differ in format: the any-format instance unless they all share a compiled-in pair)
-    TcKernel kern = tc_kernel_for(jobs_host[0].kv.s[0].bits, jobs_host[0].kv.s[1].bits);
+    TcKernel kern = tc_kernel_for(jobs_host[0].kv.s[0].bits, jobs_host[0].kv.s[1].bits, true);
     for (int j = 1; j < njobs; j++)
-        if (jobs_host[j].kv.s[0].bits != jobs_host[0].kv.s[0].bits || jobs_host[j].kv.s[1].bits != jobs_host[0].kv.s[1].bits) kern = tc::attn_tc_kernel<0, 0>;
+        if (jobs_host[j].kv.s[0].bits != jobs_host[0].kv.s[0].bits || jobs_host[j].kv.s[1].bits != jobs_host[0].kv.s[1].bits) kern = tc::attn_tc_kernel<0, 0, true>;
     int grid = 0; // (the jobs' CTAs as step_batch planned them: titem0, cpi)
     for (int j = 0; j < njobs; j++) {
         const int cpi = std::max(jobs_host[j].cpi, 1);
