@@ -52,7 +52,7 @@ NH, NKV, HD = 24, 4, 256
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at this workload's shapes, from an ncu capture of the
 # one-layer case of this benchmark (a launch of the 16-layer run processes the same one layer); NCU_TRAFFIC_FROM says which
 NCU_TRAFFIC_BYTES = 164.2e6
-NCU_TRAFFIC_FROM = "ncu capture of `bench.py --layers 1 --steps 2 --warmup 3 --no-cpu`, kernel attn_tc_kernel<5, 6>, one launch"
+NCU_TRAFFIC_FROM = "ncu capture of `bench.py --layers 1 --steps 2 --warmup 3 --no-cpu`, kernel attn_tc_kernel<5, 6> (since compiled as the one-job instance attn_tc_kernel<5, 6, false>, same code), one launch"
 WORKLOAD = "config2: 16 attention layers, 101,600 positions, preset F layout K5r/V6 + q8_0 window 2048, 8 queries/step, streaming append+spill+attend"
 REPEATS = 5  # the timed K-step loop is run this many times; the line's value is the median run
 
@@ -675,7 +675,7 @@ def main():
             "hbm_gbs_step": step_bytes / (ms * 1e-3) / 1e9 * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES if full else None, "traffic_from": NCU_TRAFFIC_FROM if full else None,
-                         "kernel": "attn_tc_kernel<5, 6> (merge in its tail)", "us_per_launch": att_us, "us_per_launch_from": att_from, "bytes_per_launch": att_bytes, "peak_source": peak_src},
+                         "kernel": "attn_tc_kernel<5, 6, false> (the one-job instance; merge in its tail)", "us_per_launch": att_us, "us_per_launch_from": att_from, "bytes_per_launch": att_bytes, "peak_source": peak_src},
             "e2e": {"value": 1e3 * ms_e2e / (layers * args.steps), "unit": "us/layer",
                     "h2d_bytes_per_step": int(layers * (2 * T_STEP * NKV * HD * 2 + T_STEP * NH * HD * 2)),
                     "d2h_bytes_per_step": int(layers * T_STEP * NH * HD * 4)},
